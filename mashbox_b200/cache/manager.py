@@ -1,8 +1,10 @@
 """The cache manager: keys and values in pages with a block table per request, and slots for fixed-size state.
 
-Layers whose mixers keep the same thing form a *group* (all keys of every position; the keys of a window; nothing).
-Each group has its own pool of pages and its own block tables, so a group with a window gives pages back as soon as
-the window has passed them while a full group keeps them until the request ends.  What a mixer keeps per position is
+Layers whose mixers keep the same thing form a *group* (all keys of every position; the keys of a window; the keys of
+the block of positions a query lies in; nothing).  Each group has its own pool of pages and its own block tables, so a
+group with a window gives pages back as soon as the window has passed them, a group whose queries see only their own
+block of `window` positions (kind "chunk") as soon as a request has entered the next block, while a full group keeps
+them until the request ends.  What a mixer keeps per position is
 its own business: a need lists the tensors (heads, width) one position holds -- keys and values of equal shape for
 attention, one latent vector for a mixer that keeps such, keys and values of different widths -- and the group gets one
 pool per listed tensor, (layers, pages, heads, page_size, width), so one head of one page is contiguous.  A page of a
@@ -29,11 +31,28 @@ from .pages import Pool
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """What one mixer keeps per position: kind "full" (every position) or "window" (the last `window` positions), and
+    """What one mixer keeps per position: kind "full" (every position), "window" (the last `window` positions) or
+    "chunk" (the positions of the query's own block of `window` positions, blocks counted from position 0), and
     `tensors`, one (heads, width) per tensor a position holds, each stored in a pool of its own."""
     kind: str
     tensors: tuple
     window: Optional[int] = None
+
+    def merged(self, other):
+        """-> the need that serves both mixers when they share one cache (one writes it, the other reads it), or None
+        when they keep different tensors.  Equal needs stay; blocks of which one size divides the other keep the
+        larger block (its start is never later); anything else keeps every position."""
+        if other is None or self.tensors != other.tensors:
+            return None
+        if self == other:
+            return self
+        if self.kind == other.kind == "chunk":
+            big, small = max(self.window, other.window), min(self.window, other.window)
+            if big % small == 0:
+                return CacheNeed("chunk", self.tensors, big)
+        if self.kind == other.kind == "window":
+            return CacheNeed("window", self.tensors, max(self.window, other.window))
+        return CacheNeed("full", self.tensors, None)
 
     @classmethod
     def keys_and_values(cls, kv_heads, head_dim, window=None):
@@ -44,7 +63,9 @@ class CacheNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """Fixed-size state one mixer keeps per request: a tensor of `shape` and dtype name per state slot."""
+    """Fixed-size state one layer keeps per request: a tensor of `shape` and dtype name per state slot.  A layer whose
+    parts keep several things (the last inputs of its short convolutions, say) asks for one flat tensor and hands each
+    part a view of its own stretch."""
     shape: tuple
     dtype: str = "float32"
 
@@ -80,7 +101,8 @@ class CacheManager:
         for cid, need in needs.items():
             if need is None:
                 continue
-            if need.kind not in ("full", "window") or (need.kind == "window" and not need.window) or not need.tensors \
+            if need.kind not in ("full", "window", "chunk") or (need.kind != "full" and not need.window) \
+                    or not need.tensors \
                     or any(len(t) != 2 or min(t) < 1 for t in need.tensors):
                 raise CacheError(f"cache need {need} is not understood")
             by_need.setdefault(need, []).append(cid)
@@ -138,6 +160,8 @@ class CacheManager:
 
     def _first_needed(self, g, length):
         """first block a query at position >= length can still read in group g"""
+        if g.need.kind == "chunk":
+            return (length // g.need.window * g.need.window) // self.page_size
         if g.need.kind != "window":
             return 0
         return max(0, length - g.need.window + 1) // self.page_size
@@ -229,11 +253,12 @@ class CacheManager:
     def pages_to_hold(self, tokens, portion):
         """-> per group, the most pages a request of `tokens` tokens holds at any time when it is fed in portions of at
         most `portion` tokens: every page of a full group; of a window group only those the window and one portion
-        reach (what lies behind the window is given back at every commit)"""
+        reach (what lies behind the window is given back at every commit); a chunk group likewise, with its block of
+        positions in the window's place"""
         whole = -(-int(tokens) // self.page_size)
         out = []
         for g in self.groups:
-            if g.need.kind == "window":
+            if g.need.kind in ("window", "chunk"):
                 out.append(min(whole, -(-(g.need.window - 1 + int(portion)) // self.page_size) + 1))
             else:
                 out.append(whole)

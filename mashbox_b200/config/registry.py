@@ -1,4 +1,4 @@
-"""The one registry from an architecture's name (config.json `architectures[0]`) to its model.
+"""The one registry from an architecture's name (config.json `architectures[0]`, or `architecture`) to its model.
 
 An entry holds: the typed configuration class (from_hf / to_hf), model_spec(config) -> ModelSpec (the layers as data),
 canonical_names(config) -> the function that maps stored tensor names to canonical ones, and stored_tensors(config) ->
@@ -38,7 +38,7 @@ def architecture(name) -> Architecture:
 
 def read_config(cfg: dict):
     """config.json as a dict -> (Architecture, typed configuration)"""
-    archs = cfg.get("architectures") or []
+    archs = cfg.get("architectures") or ([cfg["architecture"]] if cfg.get("architecture") else [])
     if not archs:
         raise ConfigError("config.json has no `architectures` entry")
     entry = architecture(archs[0])
@@ -53,8 +53,12 @@ def _builtin():
     if _done:
         return
     _done = True
-    from ..models import llama
+    from ..models import llama, luzosun
     from .llama import LlamaConfig
+    from .luzosun import LuzosunConfig
+    if "Luzosun" not in ARCHITECTURES:
+        register_architecture(Architecture("Luzosun", LuzosunConfig, luzosun.model_spec, luzosun.canonical_names,
+                                           luzosun.stored_tensors))
     for name in ("LlamaForCausalLM", "MistralForCausalLM"):
         if name not in ARCHITECTURES:
             register_architecture(Architecture(name, LlamaConfig, llama.model_spec, llama.canonical_names,

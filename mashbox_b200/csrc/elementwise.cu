@@ -34,10 +34,10 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
 }
 
 // ------------------------------------------------------------------------------------------------ embedding
-// x[n, :] = table[tok[n], :] into the float residual stream.
+// x[n, :] = table[tok[n], :] * scale into the float residual stream.
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tok, const T* __restrict__ table, float* __restrict__ x,
-                             int D, int V, int* err) {
+                             int D, int V, float scale, int* err) {
     const int n = blockIdx.x;
     int t = tok[n];
     if (t < 0 || t >= V) {
@@ -46,14 +46,14 @@ __global__ void embed_kernel(const int* __restrict__ tok, const T* __restrict__ 
         return;
     }
     const T* row = table + (size_t)t * D;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) x[(size_t)n * D + d] = mb_load(row + d);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) x[(size_t)n * D + d] = mb_load(row + d) * scale;
 }
 
 
 // the same with 128-bit accesses, for widths that are a multiple of 8
 template <typename T>
 __global__ void embed_vec_kernel(const int* __restrict__ tok, const T* __restrict__ table, float* __restrict__ x,
-                                 int D, int V, int* err) {
+                                 int D, int V, float scale, int* err) {
     const int n = blockIdx.x;
     const int t = tok[n];
     const bool ok = t >= 0 && t < V;
@@ -61,8 +61,11 @@ __global__ void embed_vec_kernel(const int* __restrict__ tok, const T* __restric
     const T* row = table + (size_t)(ok ? t : 0) * D;
     for (int c = threadIdx.x; c < D / 8; c += blockDim.x) {
         float v[8];
-        if (ok) load8(row + c * 8, v);
-        else {
+        if (ok) {
+            load8(row + c * 8, v);
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] *= scale;
+        } else {
 #pragma unroll
             for (int i = 0; i < 8; i++) v[i] = 0.0f;
         }
@@ -159,6 +162,112 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict_
             for (int e = 0; e < 8; e++) g[e] = v[j][e] * inv * g[e];
             store8(o + c * 8, g);
         }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ add + two RMSNorms
+// For a block whose mixer and feed-forward read the same stream through norms of their own: v = x[r] (+ d1[r]) (+ d2[r])
+// -- the two outputs of the block before, added into the float stream here -- written back to x unless rows picks
+// rows; out1 = v * rsqrt(mean(v^2) + eps) * w1 and, when w2 is given, out2 = the same with w2: one pass over x, one sum
+// of squares.  One block per output row; D a multiple of 8 takes 128-bit accesses.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) add_rmsnorm_pair_kernel(float* __restrict__ x, const T* __restrict__ d1,
+                                                              const T* __restrict__ d2, const int* __restrict__ rows,
+                                                              const float* __restrict__ w1, const float* __restrict__ w2,
+                                                              float eps, T* __restrict__ out1, T* __restrict__ out2,
+                                                              int D) {
+    __shared__ float scratch[32];
+    const int i = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    float* xr = x + r * D;
+    const T* a = d1 ? d1 + r * D : nullptr;
+    const T* b = d2 ? d2 + r * D : nullptr;
+    const bool keep = !rows && (a || b);
+    float ss = 0.0f;
+    if (VEC) {
+        for (int c = threadIdx.x; c < D / 8; c += 256) {
+            float v[8], t[8];
+            load8(xr + c * 8, v);
+            if (a) {
+                load8(a + c * 8, t);
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] += t[e];
+            }
+            if (b) {
+                load8(b + c * 8, t);
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] += t[e];
+            }
+            if (keep) store8(xr + c * 8, v);
+#pragma unroll
+            for (int e = 0; e < 8; e++) ss = fmaf(v[e], v[e], ss);
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += 256) {
+            float v = xr[d];
+            if (a) v += mb_load(a + d);
+            if (b) v += mb_load(b + d);
+            if (keep) xr[d] = v;
+            ss = fmaf(v, v, ss);
+        }
+    }
+    ss = mb_block_sum(ss, scratch);             // its barriers also order the writes of x above before the reads below
+    const float inv = rsqrtf(ss / (float)D + eps);
+    const bool again = rows && (a || b);        // x was not updated: form the sum once more
+    if (VEC) {
+        for (int c = threadIdx.x; c < D / 8; c += 256) {
+            float v[8], t[8], g[8];
+            load8(xr + c * 8, v);
+            if (again && a) {
+                load8(a + c * 8, t);
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] += t[e];
+            }
+            if (again && b) {
+                load8(b + c * 8, t);
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] += t[e];
+            }
+            load8(w1 + c * 8, g);
+#pragma unroll
+            for (int e = 0; e < 8; e++) t[e] = v[e] * inv * g[e];
+            store8(out1 + (size_t)i * D + c * 8, t);
+            if (w2) {
+                load8(w2 + c * 8, g);
+#pragma unroll
+                for (int e = 0; e < 8; e++) t[e] = v[e] * inv * g[e];
+                store8(out2 + (size_t)i * D + c * 8, t);
+            }
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += 256) {
+            float v = xr[d];
+            if (again && a) v += mb_load(a + d);
+            if (again && b) v += mb_load(b + d);
+            mb_store(out1 + (size_t)i * D + d, v * inv * w1[d]);
+            if (w2) mb_store(out2 + (size_t)i * D + d, v * inv * w2[d]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ xIELU
+// out = ap * z^2 + z / 2 for z > 0, an * (exp(z) - 1 - z) + z / 2 otherwise; ap and an are the layer's two numbers as
+// the host made them (softplus of the stored ones, the second plus one half).  Float arithmetic.
+__device__ __forceinline__ float xielu(float z, float ap, float an) {
+    return z > 0.0f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+}
+template <typename T, bool VEC>
+__global__ void xielu_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total, float ap, float an) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (VEC) {
+        if (i * 8 >= total) return;
+        float v[8];
+        load8(in + i * 8, v);
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] = xielu(v[e], ap, an);
+        store8(out + i * 8, v);
+    } else if (i < total) {
+        mb_store(out + i, xielu(mb_load(in + i), ap, an));
     }
 }
 
@@ -363,18 +472,21 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out,
 
 // ------------------------------------------------------------------------------------------------ launchers
 template <typename T>
-static int embed_launch(const int* tok, const void* table, float* x, int N, int D, int V, int* err, cudaStream_t st) {
+static int embed_launch(const int* tok, const void* table, float* x, int N, int D, int V, float scale, int* err,
+                        cudaStream_t st) {
     if (N == 0) return 0;
-    if (D % 8 == 0) embed_vec_kernel<T><<<N, 128, 0, st>>>(tok, (const T*)table, x, D, V, err);
-    else embed_kernel<T><<<N, 256, 0, st>>>(tok, (const T*)table, x, D, V, err);
+    if (D % 8 == 0) embed_vec_kernel<T><<<N, 128, 0, st>>>(tok, (const T*)table, x, D, V, scale, err);
+    else embed_kernel<T><<<N, 256, 0, st>>>(tok, (const T*)table, x, D, V, scale, err);
     MB_LAUNCH_CHECK();
     return 0;
 }
-MB_API int mb_embed_f32(const int* tok, const void* table, float* x, int N, int D, int V, int* err, cudaStream_t st) {
-    return embed_launch<float>(tok, table, x, N, D, V, err, st);
+MB_API int mb_embed_f32(const int* tok, const void* table, float* x, int N, int D, int V, float scale, int* err,
+                        cudaStream_t st) {
+    return embed_launch<float>(tok, table, x, N, D, V, scale, err, st);
 }
-MB_API int mb_embed_bf16(const int* tok, const void* table, float* x, int N, int D, int V, int* err, cudaStream_t st) {
-    return embed_launch<__nv_bfloat16>(tok, table, x, N, D, V, err, st);
+MB_API int mb_embed_bf16(const int* tok, const void* table, float* x, int N, int D, int V, float scale, int* err,
+                         cudaStream_t st) {
+    return embed_launch<__nv_bfloat16>(tok, table, x, N, D, V, scale, err, st);
 }
 
 template <typename T>
@@ -395,6 +507,46 @@ MB_API int mb_add_rmsnorm_f32(float* x, const void* delta, const float* dbias, c
 MB_API int mb_add_rmsnorm_bf16(float* x, const void* delta, const float* dbias, const int* rows, const float* w,
                                float eps, void* out, int n_out, int D, cudaStream_t st) {
     return add_rmsnorm_launch<__nv_bfloat16>(x, delta, dbias, rows, w, eps, out, n_out, D, st);
+}
+
+template <typename T>
+static int add_rmsnorm_pair_launch(float* x, const void* d1, const void* d2, const int* rows, const float* w1,
+                                   const float* w2, float eps, void* out1, void* out2, int n_out, int D, cudaStream_t st) {
+    if (n_out == 0) return 0;
+    if (w2 && !out2) return -2;
+    if (D % 8 == 0)
+        add_rmsnorm_pair_kernel<T, true><<<n_out, 256, 0, st>>>(x, (const T*)d1, (const T*)d2, rows, w1, w2, eps, (T*)out1,
+                                                                (T*)out2, D);
+    else
+        add_rmsnorm_pair_kernel<T, false><<<n_out, 256, 0, st>>>(x, (const T*)d1, (const T*)d2, rows, w1, w2, eps,
+                                                                 (T*)out1, (T*)out2, D);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+MB_API int mb_add_rmsnorm_pair_f32(float* x, const void* d1, const void* d2, const int* rows, const float* w1,
+                                   const float* w2, float eps, void* out1, void* out2, int n_out, int D, cudaStream_t st) {
+    return add_rmsnorm_pair_launch<float>(x, d1, d2, rows, w1, w2, eps, out1, out2, n_out, D, st);
+}
+MB_API int mb_add_rmsnorm_pair_bf16(float* x, const void* d1, const void* d2, const int* rows, const float* w1,
+                                    const float* w2, float eps, void* out1, void* out2, int n_out, int D, cudaStream_t st) {
+    return add_rmsnorm_pair_launch<__nv_bfloat16>(x, d1, d2, rows, w1, w2, eps, out1, out2, n_out, D, st);
+}
+
+template <typename T>
+static int xielu_launch(const void* in, void* out, long long total, float ap, float an, cudaStream_t st) {
+    if (total <= 0) return 0;
+    const bool vec = total % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0;
+    const long long items = vec ? total / 8 : total;
+    if (vec) xielu_kernel<T, true><<<(unsigned)((items + 255) / 256), 256, 0, st>>>((const T*)in, (T*)out, (size_t)total, ap, an);
+    else xielu_kernel<T, false><<<(unsigned)((items + 255) / 256), 256, 0, st>>>((const T*)in, (T*)out, (size_t)total, ap, an);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+MB_API int mb_xielu_f32(const void* in, void* out, long long total, float ap, float an, cudaStream_t st) {
+    return xielu_launch<float>(in, out, total, ap, an, st);
+}
+MB_API int mb_xielu_bf16(const void* in, void* out, long long total, float ap, float an, cudaStream_t st) {
+    return xielu_launch<__nv_bfloat16>(in, out, total, ap, an, st);
 }
 
 MB_PDL_SWITCH(mb_elementwise_set_pdl)

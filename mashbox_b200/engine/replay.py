@@ -24,11 +24,13 @@ from .runner import ModelRunner
 LIVE_REQUESTS = 8
 
 
-def make_runner(model_dir, dtype, max_tokens, page_size=16, device="cuda:0", options=None, log=None):
+def make_runner(model_dir, dtype, max_tokens, page_size=16, device="cuda:0", options=None, log=None,
+                max_requests=LIVE_REQUESTS):
     """max_tokens: the most tokens live requests hold at any time, each request rounded up to a multiple of 64; the
-    pool is made for exactly this many, so pages are used again."""
+    pool is made for exactly this many, so pages are used again.  max_requests: rows of the block tables and state
+    slots, so the most requests live at any time."""
     tokens = -(-int(max_tokens) // 64) * 64
-    cfg = EngineConfig(dtype=dtype, page_size=page_size, max_tokens=tokens, max_requests=LIVE_REQUESTS,
+    cfg = EngineConfig(dtype=dtype, page_size=page_size, max_tokens=tokens, max_requests=int(max_requests),
                        max_tokens_per_step=max(tokens, 64), chunk=max(tokens, 64), device=device)
     model = load_model(model_dir, dtype=dtype, device=device, log=log)
     return ModelRunner(model, cfg, options)
@@ -76,12 +78,13 @@ def main(argv=None):
     ap.add_argument("--max-tokens", required=True, type=int,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--requests", type=int, default=4, help="most requests live at any time (state slots)")
     ap.add_argument("--trace", action="store_true",
                     help="also write <step>.lh.json: [hash of the logits, gap between the two largest] per wanted row")
     a = ap.parse_args(argv)
     os.makedirs(a.out, exist_ok=True)
     print(f"trace_run: loading {a.model} ({a.dtype})", file=sys.stderr, flush=True)
-    runner = make_runner(a.model, a.dtype, a.max_tokens, a.page_size)
+    runner = make_runner(a.model, a.dtype, a.max_tokens, a.page_size, max_requests=a.requests)
     print("trace_run: ready", file=sys.stderr, flush=True)
     for line in sys.stdin:
         line = line.strip()

@@ -50,19 +50,29 @@ class Model:
         return math.lcm(*[max(1, int(getattr(p, "portion_alignment", 1))) for p in self.parts()])
 
     def cache_needs(self):
-        """-> ({cache id: CacheNeed or None}, {cache id: StateNeed}) from the schedule: the run that writes a cache
-        says what it holds; a run that only reads it must want the same."""
+        """-> ({cache id: CacheNeed or None}, {state id: StateNeed}) from the schedule: the runs that touch a cache say
+        what it holds (the same tensors; windows and blocks are merged so that every reader finds its keys)."""
         needs, states = {}, {}
         for run in self.schedule:
+            block = self.layers[run.layer]
+            # a block that holds more state-carrying parts than its mixer answers for the whole layer
+            state = block.state_need() if hasattr(block, "state_need") else block.mixer.state_need()
+            if state is not None:
+                sid = run.state_id
+                if sid is None:
+                    raise ConfigError(f"layer {run.layer} carries state but its run names neither a cache nor a state id")
+                if sid in states:
+                    raise ConfigError(f"state {sid} belongs to two runs")
+                states[sid] = state
             if run.cache is None:
                 continue
-            mixer = self.layers[run.layer].mixer
-            need, state = mixer.cache_need(), mixer.state_need()
+            need = block.mixer.cache_need()
             if run.cache in needs and needs[run.cache] != need:
-                raise ConfigError(f"cache {run.cache} is used by mixers that keep different things")
+                # a cache that several mixers use keeps what serves them all
+                need = need.merged(needs[run.cache]) if need is not None else None
+                if need is None:
+                    raise ConfigError(f"cache {run.cache} is used by mixers that keep different things")
             needs[run.cache] = need
-            if state is not None:
-                states[run.cache] = state
         written = {r.cache for r in self.schedule if r.write}
         for run in self.schedule:
             if run.cache is not None and run.cache not in written:
@@ -74,7 +84,8 @@ class Model:
         for run in self.schedule:
             if run.layer not in seen:
                 seen.add(run.layer)
-                self.layers[run.layer].mixer.prepare(ctx)
+                block = self.layers[run.layer]
+                (block if hasattr(block, "prepare") else block.mixer).prepare(ctx)
 
     def forward(self, ctx):
         """Runs the step's tokens through the schedule.  -> float32 logits (n_out, vocab) at the wanted tokens."""

@@ -142,13 +142,13 @@ def check_error_word(err):
 
 
 # ------------------------------------------------------------------------------------------------ elementwise
-def embed(tokens, table, x, err):
-    """x[n] = table[tokens[n]] into the float32 residual stream x (N, D)."""
+def embed(tokens, table, x, err, scale=1.0):
+    """x[n] = table[tokens[n]] * scale into the float32 residual stream x (N, D)."""
     _cuda(tokens, table, x)
     N, D = x.shape
     f = _fn("elementwise", "mb_embed_" + _suffix(table.dtype),
-            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(f(_p(tokens), _p(table), _p(x), N, D, table.shape[0], _p(err), _stream()), "embed")
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(f(_p(tokens), _p(table), _p(x), N, D, table.shape[0], float(scale), _p(err), _stream()), "embed")
 
 
 def add_rmsnorm(x, delta, delta_bias, weight, eps, out, rows=None):
@@ -161,6 +161,62 @@ def add_rmsnorm(x, delta, delta_bias, weight, eps, out, rows=None):
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p])
     _check(f(_p(x), _p(delta), _p(delta_bias), _p(rows), _p(weight), float(eps), _p(out), n_out, D, _stream()),
            "add_rmsnorm")
+
+
+def add_rmsnorm_pair(x, delta1, delta2, weight1, weight2, eps, out1, out2=None, rows=None):
+    """v = x (+ delta1) (+ delta2), written back to x unless rows is given; out1 = v * rsqrt(mean(v^2) + eps) * weight1
+    and, with weight2, out2 = the same with weight2 (one pass, one sum of squares).  x (N, D) float32; deltas and outs in
+    the activation dtype; weights float32; rows int32 indexes."""
+    _cuda(x, delta1, delta2, weight1, weight2, out1, out2, rows)
+    D = x.shape[1]
+    f = _fn("elementwise", "mb_add_rmsnorm_pair_" + _suffix(out1.dtype),
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+             c_void_p])
+    _check(f(_p(x), _p(delta1), _p(delta2), _p(rows), _p(weight1), _p(weight2), float(eps), _p(out1), _p(out2),
+             out1.shape[0], D, _stream()), "add_rmsnorm_pair")
+
+
+def xielu(z, out, ap, an):
+    """out = ap z^2 + z/2 where z > 0, an (exp(z) - 1 - z) + z/2 elsewhere; z and out (N, F) in the activation dtype"""
+    _cuda(z, out)
+    f = _fn("elementwise", "mb_xielu_" + _suffix(out.dtype),
+            [c_void_p, c_void_p, ctypes.c_longlong, c_float, c_float, c_void_p])
+    _check(f(_p(z), _p(out), z.numel(), float(ap), float(an), _stream()), "xielu")
+
+
+# ------------------------------------------------------------------------------------------------ short convolutions
+def short_conv(x, w, state, seq, out, residual=False):
+    """out = (x if residual) + causal_conv(x): x, out (N, C) in the activation dtype, w (C, taps) float32, one filter per
+    channel.  state (slots, taps - 1, C) float32 (a view: rows C apart, slots state.stride(0) apart) holds every
+    sequence's last taps - 1 inputs and is replaced by this step's.  seq = (tok_seq, q_start, q_len, state_slot) int32
+    device arrays: per token its sequence's index in the step; per sequence its first token, length and state slot."""
+    _cuda(x, w, state, out, *seq)
+    N, C = x.shape
+    taps = w.shape[1]
+    f = _fn("short_conv", "mb_short_conv_" + _suffix(x.dtype),
+            [c_void_p, c_void_p, c_void_p, ctypes.c_longlong] + [c_void_p] * 5 + [c_int] * 4 + [c_void_p])
+    _check(f(_p(x), _p(w), _p(state), state.stride(0) if state is not None else 0, *[_p(t) for t in seq], _p(out), N, C,
+             taps, 1 if residual else 0, _stream()), "short_conv")
+
+
+def conv_rope_kv_write(qkv, bias, w, state, seq, positions, tok_row, table, q_out, kpool, vpool, freqs, QU, KU, VH, dim,
+                       vdim, kper, RD, page, num_pages, err):
+    """What follows a fused q/k/v product whose outputs pass a short convolution: rows of qkv (N, (QU + KU) dim + VH
+    vdim) = [query units | key units | value heads] get their bias, are convolved over time per channel (w (C, taps)
+    float32 or None; state and seq as short_conv), the first RD dims of every query and key unit are rotated by the
+    token's position (dim i with dim i + RD/2; freqs (RD/2,) float32 or None), queries go to q_out (N, QU dim), keys
+    and values into the pages of the token's position: kpool (pages, VH, page, kper dim) takes `kper` key units per kv
+    head, vpool (pages, VH, page, vdim).  KU = VH = 0: the rows hold queries only."""
+    _cuda(qkv, bias, w, state, positions, tok_row, table, q_out, kpool, vpool, freqs, *seq)
+    N = qkv.shape[0]
+    taps = 1 if w is None else w.shape[1]
+    f = _fn("short_conv", "mb_conv_rope_kv_write_" + _suffix(qkv.dtype),
+            [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong] + [c_void_p] * 7 + [c_int] + [c_void_p] * 4
+            + [c_int] * 11 + [c_void_p, c_void_p])
+    _check(f(_p(qkv), _p(bias), _p(w), _p(state), state.stride(0) if state is not None else 0, *[_p(t) for t in seq],
+             _p(positions), _p(tok_row), _p(table), table.shape[1] if table is not None else 0, _p(q_out), _p(kpool),
+             _p(vpool), _p(freqs), N, QU, KU, VH, dim, vdim, kper, RD, page, num_pages, taps, _p(err), _stream()),
+           "conv_rope_kv_write")
 
 
 def rope_kv_write(qkv, bias, positions, tok_seq, table, kpool, vpool, freqs, H, KV, HD, RD, pairing, page, num_pages,
@@ -487,6 +543,19 @@ def attention_simple(q, q_stride, out, positions, tok_seq, table, kpool, vpool, 
             + [c_float, c_void_p, c_void_p])
     _check(f(_p(q), q_stride, _p(out), _p(positions), _p(tok_seq), _p(table), table.shape[1], _p(kpool), _p(vpool), N,
              H, KV, HD, page, num_pages, window or 0, float(scale), _p(err), _stream()), "attention_simple")
+
+
+def attention_diff_simple(q, out, positions, tok_row, table, kpool, vpool, H, G, dim, vdim, page, num_pages, chunk,
+                          scale, lam, gain, eps, err):
+    """Differential attention, plain kernel: q (N, H * 2 dim) holds two maps per head, kpool (pages, G, page, 2 dim),
+    vpool (pages, G, page, vdim) -> out (N, H vdim) = rmsnorm_head(a_0 - lam a_1) * gain, a_m the softmax attention of
+    map m over the keys of the query's own block of `chunk` positions (0: all) up to its position."""
+    _cuda(q, out, positions, tok_row, table, kpool, vpool)
+    f = _fn("attention_diff", "mb_attn_diff_simple_" + _suffix(q.dtype),
+            [c_void_p] * 5 + [c_int, c_void_p, c_void_p] + [c_int] * 8 + [c_float] * 4 + [c_void_p, c_void_p])
+    _check(f(_p(q), _p(out), _p(positions), _p(tok_row), _p(table), table.shape[1], _p(kpool), _p(vpool), q.shape[0], H,
+             G, dim, vdim, page, num_pages, int(chunk or 0), float(scale), float(lam), float(gain), float(eps), _p(err),
+             _stream()), "attention_diff_simple")
 
 
 def attention_mma_supports(HD):

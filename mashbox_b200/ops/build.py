@@ -30,6 +30,8 @@ LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "gemm_stream": ("gemm_stream.cu", []),
     "gemv": ("gemv.cu", []),
     "attention_simple": ("attention_simple.cu", []),
+    "attention_diff": ("attention_diff.cu", []),
+    "short_conv": ("short_conv.cu", []),
     "attention_mma": ("attention_mma.cu", []),                         # head sizes 16, 32, 64, 128
     "attention_mma_wide": ("attention_mma.cu", ["-DMB_ATTN_WIDE"]),    # the other multiples of 16 up to 256
     "attention_tma": ("attention_tma.cu", []),

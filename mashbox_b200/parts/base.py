@@ -11,11 +11,14 @@ Interfaces (all tensors on the device; N = tokens of the step, D = the part's wi
                 (delta, bias or None) from the sublayer before, added into x first (in place unless rows picks rows).
   Position      wants() -> [Want];  bind(tensors, env);  rotation() -> (freqs, rotary_dim, pairing) for the fused
                 rotate-and-store kernel, or None with apply(ctx, qkv, heads) doing its own work in place.
-  Mixer         wants(prefix);  bind;  cache_need() -> CacheNeed or None;  state_need() -> StateNeed or None;
+  Mixer         wants(prefix);  bind;  cache_need() -> CacheNeed or None;  state_need() -> StateNeed or None
+                (a block with state-carrying parts of its own answers state_need() for the whole layer instead);
                 prepare(ctx) (host-side plan arrays into ctx.inputs, before the upload);
                 forward(ctx, h, run) -> (delta (N, D), bias or None).  run says which cache id it reads and whether
                 it writes it.
   FeedForward   wants(prefix);  bind;  forward(ctx, h) -> (delta, bias or None)
+  Conv          wants();  bind;  state_floats() -> float32 values it keeps per request (its layer's block gives it a
+                stretch of the layer's state: state_offset);  prepare(ctx);  forward(ctx, h, state_id) -> h'
   Block         built from the part specs in its own PartSpec and the layer's prefix;  parts() -> every part it
                 holds;  mixer: the part that owns the cache of a run;  forward(ctx, x, pending, run) -> pending
 
@@ -66,10 +69,18 @@ class LayerSpec:
 class LayerRun:
     """One entry of the schedule: run layer `layer`; its mixer reads cache `cache` (None: it keeps nothing) and writes
     this step's keys and values there when `write` is set.  Two entries may name one layer (it runs twice, each time
-    with the cache id its entry gives) and an entry may read a cache another layer wrote (write=False)."""
+    with the cache id its entry gives) and an entry may read a cache another layer wrote (write=False).  Fixed-size
+    state of the run (what its parts carry from step to step besides the cache) is kept under `state`; None: under
+    the cache id, as a run that owns its cache wants it.  A run that borrows a cache but carries state of its own
+    names an id no other run has."""
     layer: int
     cache: int = None
     write: bool = True
+    state: int = None
+
+    @property
+    def state_id(self):
+        return self.cache if self.state is None else self.state
 
 
 @dataclass
@@ -83,13 +94,13 @@ class ModelSpec:
     head: PartSpec
 
 
-NORMS, POSITIONS, MIXERS, FEED_FORWARDS, BLOCKS, EMBEDDINGS, HEADS = {}, {}, {}, {}, {}, {}, {}
+NORMS, POSITIONS, MIXERS, FEED_FORWARDS, BLOCKS, EMBEDDINGS, HEADS, CONVS = {}, {}, {}, {}, {}, {}, {}, {}
 _TABLES = {"norm": NORMS, "position": POSITIONS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS, "block": BLOCKS,
-           "embedding": EMBEDDINGS, "head": HEADS}
+           "embedding": EMBEDDINGS, "head": HEADS, "conv": CONVS}
 
 
 def register(family, kind, cls):
-    """Adds a part kind: family is norm | position | mixer | feed_forward | block | embedding | head."""
+    """Adds a part kind: family is norm | position | mixer | feed_forward | block | embedding | head | conv."""
     _TABLES[family][kind] = cls
     return cls
 

@@ -4,6 +4,7 @@
 sublayer returns its output as `pending` and the next norm adds it into the float32 residual stream in the same kernel
 that normalises, so the block returns the feed-forward's output still pending.
 """
+from ..errors import ConfigError
 from .base import make, register
 
 
@@ -46,3 +47,72 @@ class PreNormBlock:
 
 
 register("block", "prenorm", PreNormBlock)
+
+
+class ParallelBlock:
+    """x += mixer(conv(norm1(x))) + ffn(norm2(x)): both sublayers read the same stream, each through a norm of its own.
+
+    `mixer_conv` (optional): a short causal convolution on what the mixer reads.  `ffn` may be None.  The two outputs
+    stay pending (delta of the mixer, None, delta of the feed-forward) and the next norm kernel adds both into the
+    float32 stream; when the two norms are of one kind, width and eps, one kernel makes both from one sum of squares.
+    The layer's state (what its convolutions carry across steps) is one flat float32 tensor per request: the input
+    convolution's stretch first, then the mixer's."""
+
+    def __init__(self, prefix, mixer, norm1, norm2=None, ffn=None, mixer_conv=None, names=None):
+        n = dict(norm1="norm1", norm2="norm2", conv="canon1")
+        n.update(names or {})
+        self.norm1 = make("norm", norm1, name=prefix + n["norm1"])
+        self.conv = make("conv", mixer_conv, name=prefix + n["conv"]) if mixer_conv is not None else None
+        self.mixer = make("mixer", mixer, prefix=prefix)
+        self.ffn = make("feed_forward", ffn, prefix=prefix) if ffn is not None else None
+        self.norm2 = make("norm", norm2 or norm1, name=prefix + n["norm2"]) if self.ffn is not None else None
+        off = 0
+        for part in (self.conv, self.mixer):
+            if part is not None and hasattr(part, "state_floats"):
+                part.state_offset = off
+                off += part.state_floats()
+        self.state_total = off
+
+    @property
+    def graph_safe(self):
+        return True         # forward() depends on the batch only through the lengths of the step's arrays
+
+    def parts(self):
+        return [p for p in (self.norm1, self.conv, self.mixer, self.norm2, self.ffn) if p is not None]
+
+    def first_norm(self):
+        return self.norm1
+
+    def state_need(self):
+        from ..cache.manager import StateNeed
+        if hasattr(self.mixer, "state_floats"):
+            return StateNeed((self.state_total,), "float32") if self.state_total else None
+        if self.conv is not None and self.conv.state_floats():
+            raise ConfigError("a parallel block with an input convolution needs a mixer that says how much state it keeps")
+        return self.mixer.state_need()
+
+    def prepare(self, ctx):
+        for part in (self.conv, self.mixer):
+            if part is not None:
+                part.prepare(ctx)
+
+    def forward(self, ctx, x, pending, run):
+        ctx.after_norm = None
+        if self.ffn is not None and hasattr(self.norm1, "forward_pair") and type(self.norm2) is type(self.norm1) \
+                and (self.norm1.width, self.norm1.eps) == (self.norm2.width, self.norm2.eps):
+            a, b = self.norm1.forward_pair(ctx, x, self.norm2, pending)
+        else:
+            a = self.norm1.forward(ctx, x, pending)
+            b = self.norm2.forward(ctx, x, None) if self.ffn is not None else None
+        if self.conv is not None:
+            a = self.conv.forward(ctx, a, run.state_id)
+        delta, bias = self.mixer.forward(ctx, a, run)
+        if self.ffn is None:
+            return delta, bias
+        if bias is not None:
+            raise ConfigError("a parallel block cannot defer a bias of its mixer's output")
+        side, _ = self.ffn.forward(ctx, b, out="delta_side")
+        return delta, None, side
+
+
+register("block", "parallel", ParallelBlock)

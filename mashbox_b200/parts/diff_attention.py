@@ -1,0 +1,123 @@
+"""The differential attention mixer: two softmax attention maps per head over one set of values, their difference
+normalised per head.
+
+Every head has two maps with queries and keys of their own (rows of the q and k projections lie head by head as
+[map 0 | map 1], `dim` each) and shares its values (`vdim` wide) between them:
+
+    a_m = softmax(scale q_m K_m^T) V,    o = a_0 - lam a_1,    out = o / sqrt(mean(o^2) + eps) * (1 - delta)
+
+with lam = exp(lq1 . lk1) - exp(lq2 . lk2) + delta, one number for the layer, made at load in float64 from its four
+vectors.  Query head h reads kv head h // (H / G).  Options, each a constructor parameter: biases on q/k/v; a short
+causal convolution over time on every channel of q, k and v right after the projection (`taps`; the last taps - 1
+projected rows are carried in the layer's state); a rotation of the first dims of every map (`position`, a rotary
+encoding with the halves pairing); `chunk`: a query sees the keys of its own block of `chunk` positions, counted from
+the sequence's start, up to itself (None: all earlier keys); `shares_kv`: the layer has no k/v projections and reads
+the cache another layer wrote (its schedule entry names that cache), with its own queries and mask.
+
+A step: one fused q/k/v product; one kernel adds the biases, convolves, rotates, stores the keys (both maps of a kv
+head side by side) and values in their pages and the queries in a buffer; the attention kernel reads the step's own
+tokens from the cache like older ones, so whole prompts, portions and single tokens take one path; then the output
+product.  Scores, softmaxes, weighted sums, the difference and the head norm are float32.
+"""
+import math
+
+from ..cache.manager import CacheNeed, StateNeed
+from ..errors import ConfigError
+from ..weights.loader import Want
+from .base import PartSpec, make, register
+from .conv import plan_sequences, state_view, step_sequences
+
+
+class DifferentialAttention:
+    @property
+    def graph_safe(self):
+        """forward() depends on the batch only through the lengths of the step's arrays; so must the position encoding"""
+        return self.position is None or bool(getattr(self.position, "graph_safe", False))
+
+    def __init__(self, hidden, heads, kv_heads, dim, vdim, delta, eps, scale=None, bias=True, taps=1, position=None,
+                 chunk=None, shares_kv=False, prefix="", names=None):
+        self.D, self.H, self.G, self.dim, self.vdim = int(hidden), int(heads), int(kv_heads), int(dim), int(vdim)
+        if self.G < 1 or self.H % self.G:
+            raise ConfigError(f"{heads} heads do not divide into {kv_heads} kv heads")
+        self.delta, self.eps = float(delta), float(eps)
+        self.scale = float(scale) if scale else self.dim ** -0.5
+        self.bias, self.taps = bool(bias), max(1, int(taps or 1))
+        self.chunk = int(chunk) if chunk else None
+        self.shares_kv = bool(shares_kv)
+        n = dict(q="q", k="k", v="v", o="o", bias=".b", conv=".conv", lq1="lq1", lk1="lk1", lq2="lq2", lk2="lk2")
+        n.update(names or {})
+        self.n = {k: (v if k in ("bias", "conv") else prefix + v) for k, v in n.items()}
+        self.position = make("position", position) if isinstance(position, PartSpec) else position
+        self.roles = ("q",) if self.shares_kv else ("q", "k", "v")
+        self.rows = dict(q=self.H * 2 * self.dim, k=self.G * 2 * self.dim, v=self.G * self.vdim)
+        self.C = sum(self.rows[r] for r in self.roles)
+        self.state_offset = 0
+        self.w = self.b = self.wconv = self.wo = self.lam = None
+
+    # ------------------------------------------------------------------------------------------ weights
+    def wants(self):
+        out = []
+        for r in self.roles:
+            out.append(Want(self.n[r], (self.rows[r], self.D), "matrix"))
+            if self.bias:
+                out.append(Want(self.n[r] + self.n["bias"], (self.rows[r],), "vector"))
+            if self.taps > 1:
+                out.append(Want(self.n[r] + self.n["conv"], (self.rows[r], self.taps), "vector"))
+        out += [Want(self.n[v], (self.dim,), "vector") for v in ("lq1", "lk1", "lq2", "lk2")]
+        out.append(Want(self.n["o"], (self.D, self.H * self.vdim), "matrix"))
+        return out + (self.position.wants() if self.position is not None else [])
+
+    def bind(self, tensors, env):
+        import torch
+        cat = lambda suffix: torch.cat([tensors[self.n[r] + suffix] for r in self.roles], 0).contiguous()
+        self.w = cat("")
+        self.b = cat(self.n["bias"]) if self.bias else None
+        self.wconv = cat(self.n["conv"]) if self.taps > 1 else None
+        self.wo = tensors[self.n["o"]]
+        dot = lambda a, b: float((tensors[self.n[a]].double() * tensors[self.n[b]].double()).sum())
+        self.lam = math.exp(dot("lq1", "lk1")) - math.exp(dot("lq2", "lk2")) + self.delta
+        if self.position is not None:
+            self.position.bind(tensors, env)
+            rot = self.position.rotation()
+            if rot is None or rot[2] != 1 or rot[1] > self.dim:
+                raise ConfigError("the differential attention mixer rotates the first dims of a map, dim i with dim "
+                                  "i + half: its position encoding must be rotary with the halves pairing")
+
+    def cache_need(self):
+        return CacheNeed("chunk" if self.chunk else "full", ((self.G, 2 * self.dim), (self.G, self.vdim)), self.chunk)
+
+    def state_floats(self):
+        return (self.taps - 1) * self.C
+
+    def state_need(self):
+        return StateNeed((self.state_floats(),), "float32") if self.taps > 1 else None
+
+    def prepare(self, ctx):
+        plan_sequences(ctx)
+
+    # ------------------------------------------------------------------------------------------ forward
+    def forward(self, ctx, h, run):
+        ops, N = ctx.ops, ctx.N
+        H, G, dim, vdim = self.H, self.G, self.dim, self.vdim
+        if run.write == self.shares_kv:
+            raise ConfigError("a differential attention layer writes the cache it owns and only reads one it borrows")
+        qkv = ctx.ws.get("qkv", N, (self.C,), ctx.dtype)
+        ops.linear(h, self.w, out=qkv)
+        group, kpool, vpool = ctx.cache.layer_cache(run.cache)
+        table, page, pages = group.device_table, ctx.cache.page_size, ctx.cache.pool_pages
+        freqs, rd, _ = self.position.rotation() if self.position is not None else (None, 0, 1)
+        q = ctx.ws.get("diff_q", N, (H * 2 * dim,), ctx.dtype)
+        own = not self.shares_kv
+        ops.conv_rope_kv_write(qkv, self.b, self.wconv, state_view(ctx, run.state_id, self.state_offset, self.taps, self.C),
+                               step_sequences(ctx), ctx.dev("positions"), ctx.dev("tok_row"), table, q,
+                               kpool if own else None, vpool if own else None, freqs, 2 * H, 2 * G if own else 0,
+                               G if own else 0, dim, vdim, 2, rd, page, pages, ctx.err)
+        out = ctx.ws.get("attn_out", N, (H * vdim,), ctx.dtype)
+        ops.attention_diff_simple(q, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, G, dim, vdim,
+                                  page, pages, self.chunk, self.scale, self.lam, 1.0 - self.delta, self.eps, ctx.err)
+        y = ctx.ws.get("delta", N, (self.D,), ctx.dtype)
+        ops.linear(out, self.wo, out=y)
+        return y, None
+
+
+register("mixer", "differential_attention", DifferentialAttention)

@@ -6,8 +6,9 @@ from .base import register
 
 class Embedding:
     graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
-    def __init__(self, vocab, hidden, name="token_embd.weight"):
-        self.V, self.D, self.name = int(vocab), int(hidden), name
+    def __init__(self, vocab, hidden, name="token_embd.weight", scale=1.0):
+        """scale: every row is multiplied by it on its way into the stream"""
+        self.V, self.D, self.name, self.scale = int(vocab), int(hidden), name, float(scale)
         self.table = None
 
     def wants(self):
@@ -17,7 +18,7 @@ class Embedding:
         self.table = tensors[self.name]
 
     def forward(self, ctx, x):
-        ctx.ops.embed(ctx.dev("token_ids"), self.table, x, ctx.err)
+        ctx.ops.embed(ctx.dev("token_ids"), self.table, x, ctx.err, self.scale)
 
 
 class LinearHead:

@@ -1,5 +1,7 @@
 """Dense SwiGLU feed-forward: (silu(h Wg^T) * (h Wu^T)) Wd^T, silu and the product in float32
 (src/mashbox/gguf/archs/dense.py:356-357).  Gate and up weights are concatenated at load so one product makes both."""
+import math
+
 from ..weights.loader import Want
 from .base import register
 
@@ -47,3 +49,45 @@ class SwiGLU:
 
 
 register("feed_forward", "swiglu", SwiGLU)
+
+
+def _softplus(t):
+    return max(t, 0.0) + math.log1p(math.exp(-abs(t)))
+
+
+class DenseXielu:
+    """act(h Wu^T) Wd^T with the xIELU activation: act(z) = ap z^2 + z/2 for z > 0 and an (e^z - 1 - z) + z/2 otherwise,
+    ap = softplus(p), an = 1/2 + softplus(q); the layer's two numbers (p, q) are one stored tensor.  The activation is
+    float32 arithmetic on the product's outputs."""
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
+
+    def __init__(self, hidden, intermediate, prefix="", names=None):
+        self.D, self.F = int(hidden), int(intermediate)
+        n = dict(up="ffn_up.weight", down="ffn_down.weight", act="ffn_act")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.wu = self.wd = self.ap = self.an = None
+
+    def wants(self):
+        return [Want(self.names["up"], (self.F, self.D), "matrix"), Want(self.names["down"], (self.D, self.F), "matrix"),
+                Want(self.names["act"], (2,), "vector")]
+
+    def bind(self, tensors, env):
+        self.wu, self.wd = tensors[self.names["up"]], tensors[self.names["down"]]
+        p, q = (float(v) for v in tensors[self.names["act"]].double().cpu())
+        self.ap, self.an = _softplus(p), 0.5 + _softplus(q)
+
+    def forward(self, ctx, h, out="delta"):
+        """out: the workspace buffer the result is left in (a block that runs this part beside its mixer names another
+        one than the mixer's)"""
+        N = ctx.N
+        z = ctx.ws.get("ffn_up", N, (self.F,), ctx.dtype)
+        ctx.ops.linear(h, self.wu, out=z)
+        a = ctx.ws.get("ffn_act", N, (self.F,), ctx.dtype)
+        ctx.ops.xielu(z, a, self.ap, self.an)
+        y = ctx.ws.get(out, N, (self.D,), ctx.dtype)
+        ctx.ops.linear(a, self.wd, out=y)
+        return y, None
+
+
+register("feed_forward", "dense_xielu", DenseXielu)

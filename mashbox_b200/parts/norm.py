@@ -4,6 +4,7 @@ y = v * rsqrt(mean(v^2) + eps) * w with the weight multiplied as stored (src/mas
 where v is the residual stream plus the output of the sublayer before (the add of src/mashbox/gguf/archs/dense.py:348,
 357, here in float32).  One kernel reads x and the delta once, writes x back and writes y.
 """
+from ..errors import ConfigError
 from ..weights.loader import Want
 from .base import register
 
@@ -28,11 +29,32 @@ class RMSNorm:
         n_out = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.ws.get("normed" if rows is None else "normed_rows", n_out, (self.width,), ctx.dtype,
                          reserve=None if rows is None else ctx.options.get("logit_rows", 8))
-        delta, bias = pending if pending is not None else (None, None)
+        delta, bias, *more = pending if pending is not None else (None, None)
         if delta is not None:
             ctx.memo.pop("held", None)         # x changes here: what is held for it no longer describes it
-        ctx.ops.add_rmsnorm(x, delta, bias, self.weight, self.eps, out, rows)
+        if more:                                # two sublayers that ran side by side left an output each
+            if bias is not None:
+                raise ConfigError("two pending outputs cannot be combined with a pending bias")
+            ctx.ops.add_rmsnorm_pair(x, delta, more[0], self.weight, None, self.eps, out, None, rows)
+        else:
+            ctx.ops.add_rmsnorm(x, delta, bias, self.weight, self.eps, out, rows)
         return out
+
+    def forward_pair(self, ctx, x, other, pending=None):
+        """-> (this norm of x, `other`'s norm of x), x first taking in what is pending ((delta, None) or (delta, None,
+        second delta)): for two norms of one width and eps that read the same stream, one kernel and one sum of
+        squares."""
+        if other.width != self.width or other.eps != self.eps:
+            raise ConfigError("norms with different widths or eps cannot be computed as a pair")
+        delta, bias, *more = pending if pending is not None else (None, None)
+        if bias is not None:
+            raise ConfigError("a pair of norms cannot take a pending bias")
+        if delta is not None:
+            ctx.memo.pop("held", None)
+        a = ctx.ws.get("normed", x.shape[0], (self.width,), ctx.dtype)
+        b = ctx.ws.get("normed_side", x.shape[0], (self.width,), ctx.dtype)
+        ctx.ops.add_rmsnorm_pair(x, delta, more[0] if more else None, self.weight, other.weight, self.eps, a, b)
+        return a, b
 
 
 register("norm", "rms", RMSNorm)

@@ -42,7 +42,8 @@ def base_frequencies(theta, rotary_dim):
 class RotaryEncoding:
     graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
     def __init__(self, head_dim, rotary_dim, theta, scaling=None, pairing="adjacent", factors_name=None):
-        """scaling: None | ("linear", factor) | ("llama3", factor, low, high, original).  factors_name: canonical name
+        """scaling: None | ("linear", factor) | ("divide", factor) | ("llama3", factor, low, high, original); "linear"
+        multiplies every frequency by float32(1 / factor), "divide" divides it by the factor.  factors_name: canonical name
         of an optional tensor of per-pair divisors that replaces the computed llama3 factors when the file has it."""
         self.head_dim, self.rotary_dim, self.theta = int(head_dim), int(rotary_dim), float(theta)
         self.scaling = tuple(scaling) if scaling else None
@@ -60,7 +61,7 @@ class RotaryEncoding:
         multiplies by 1/factor in the same expression, dense.py:316-317)."""
         f = base_frequencies(self.theta, self.rotary_dim)
         kind = self.scaling[0] if self.scaling else None
-        if kind not in (None, "linear", "llama3"):
+        if kind not in (None, "linear", "divide", "llama3"):
             raise ValueError(self.scaling)
         if stored_factors is not None:
             f = (f / np.asarray(stored_factors, np.float32)).astype(np.float32)
@@ -69,6 +70,8 @@ class RotaryEncoding:
             f = (f / llama3_factors(self.theta, self.rotary_dim, factor, low, high, original)).astype(np.float32)
         if kind == "linear":
             f = (f * np.float32(1.0 / self.scaling[1])).astype(np.float32)
+        if kind == "divide":
+            f = (f / np.float32(self.scaling[1])).astype(np.float32)
         return f
 
     def bind(self, tensors, env):
