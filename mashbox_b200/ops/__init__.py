@@ -558,6 +558,36 @@ def attention_diff_simple(q, out, positions, tok_row, table, kpool, vpool, H, G,
              _stream()), "attention_diff_simple")
 
 
+DIFF_MMA_ROWS = 64
+
+
+def attention_diff_mma_supports(dim, vdim):
+    """the tensor-core kernel of the differential attention takes these head sizes (bfloat16 only)"""
+    return dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 128 and 16 <= vdim <= 128
+
+
+def attention_diff_mma_rows():
+    """packed query rows (tokens times the query heads of a kv head) of one work item"""
+    return DIFF_MMA_ROWS
+
+
+def attention_diff_mma(q, out, items, n_items, q_start, q_len, pos0, seq_row, table, kpool, vpool, H, G, dim, vdim, page,
+                       num_pages, chunk, scale, lam, gain, eps, err):
+    """Differential attention on tensor cores (bfloat16): the same result as attention_diff_simple.  items: n_items
+    (sequence, tile of 64 packed rows) pairs; q_start, q_len, pos0, seq_row per sequence.  The kernel is compiled for
+    the pair (dim, vdim) the first time it is asked for."""
+    _cuda(q, out, items, q_start, q_len, pos0, seq_row, table, kpool, vpool)
+    if q.dtype != torch.bfloat16 or not attention_diff_mma_supports(dim, vdim):
+        raise KernelError(f"attention_diff_mma: no kernel for {q.dtype} with head sizes {dim} and {vdim}")
+    from .build import variant
+    lib = variant(f"attention_diff_mma_{dim}_{vdim}", "attention_diff_mma.cu", [f"-DDIFF_DIM={dim}", f"-DDIFF_VD={vdim}"])
+    f = _fn(lib, "mb_attn_diff_mma", [c_void_p] * 5 + [c_int] + [c_void_p] * 5 + [c_int] * 6 + [c_float] * 4
+            + [c_void_p, c_void_p])
+    _check(f(_p(q), _p(out), _p(kpool), _p(vpool), _p(items), int(n_items), _p(q_start), _p(q_len), _p(pos0), _p(seq_row),
+             _p(table), table.shape[1], H, G, page, num_pages, int(chunk or 0), float(scale), float(lam), float(gain),
+             float(eps), _p(err), _stream()), "attention_diff_mma")
+
+
 def attention_mma_supports(HD):
     """head sizes in steps of 16 up to 256 (16, 32, 64, 128 in one library, the others in a second one)"""
     return 16 <= HD <= 256 and HD % 16 == 0

@@ -31,6 +31,9 @@ LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "gemv": ("gemv.cu", []),
     "attention_simple": ("attention_simple.cu", []),
     "attention_diff": ("attention_diff.cu", []),
+    # one library per pair of head sizes, registered when a model asks for it (variant()); these two are always built
+    "attention_diff_mma_64_128": ("attention_diff_mma.cu", ["-DDIFF_DIM=64", "-DDIFF_VD=128"]),
+    "attention_diff_mma_128_128": ("attention_diff_mma.cu", ["-DDIFF_DIM=128", "-DDIFF_VD=128"]),
     "short_conv": ("short_conv.cu", []),
     "attention_mma": ("attention_mma.cu", []),                         # head sizes 16, 32, 64, 128
     "attention_mma_wide": ("attention_mma.cu", ["-DMB_ATTN_WIDE"]),    # the other multiples of 16 up to 256
@@ -43,6 +46,14 @@ LIBRARIES = {            # library name -> (source file, extra compiler flags)
 EXTRA_SOURCES = {"sampling_noalloc": ["sampling.cu", "sampling_noalloc.h"]}      # files a library includes
 _loaded = {}
 _lock = threading.Lock()
+
+
+def variant(name, source, flags):
+    """Registers a library that is `source` compiled with extra flags (a kernel specialised for sizes a model brings)
+    under `name`, unless it is there already.  -> name"""
+    with _lock:
+        LIBRARIES.setdefault(name, (source, list(flags)))
+    return name
 
 
 def find_nvcc():

@@ -21,11 +21,24 @@ product.  Scores, softmaxes, weighted sums, the difference and the head norm are
 """
 import math
 
+import numpy as np
+
 from ..cache.manager import CacheNeed, StateNeed
 from ..errors import ConfigError
 from ..weights.loader import Want
 from .base import PartSpec, make, register
 from .conv import plan_sequences, state_view, step_sequences
+
+
+def plan_diff_tiles(q_len, pos0, group, rows):
+    """Work list of the tensor-core kernel: one (sequence, tile) pair per `rows` packed query rows -- a sequence's
+    tokens times the `group` query heads of a kv head -- the tiles that reach the most keys first.  -> flat int list"""
+    items = []
+    for s, n in enumerate(q_len):
+        for m in range(-(-n * group // rows)):
+            items.append((-min(n, (m + 1) * rows // group), s, m))
+    items.sort()
+    return [v for it in items for v in it[1:]]
 
 
 class DifferentialAttention:
@@ -92,8 +105,23 @@ class DifferentialAttention:
     def state_need(self):
         return StateNeed((self.state_floats(),), "float32") if self.taps > 1 else None
 
+    def uses_mma(self, ctx):
+        import torch
+        return (ctx.dtype == torch.bfloat16 and ctx.ops.attention_diff_mma_supports(self.dim, self.vdim)
+                and not ctx.options.get("plain_attention", False))
+
     def prepare(self, ctx):
+        """host side: the sequences' indexes for the convolution kernels and, for the tensor-core kernel, the list of
+        (sequence, row tile) work items (one list for all layers with the same number of query heads per kv head)"""
         plan_sequences(ctx)
+        if not self.uses_mma(ctx):
+            return
+        key = ("diff_tiles", self.H // self.G)
+        if key not in ctx.memo:
+            name = f"diff_tiles_{self.H // self.G}"
+            items = plan_diff_tiles(ctx.q_len, ctx.pos0, self.H // self.G, ctx.ops.attention_diff_mma_rows())
+            ctx.inputs.add(name, np.asarray(items, np.int32))
+            ctx.memo[key] = (name, len(items) // 2)
 
     # ------------------------------------------------------------------------------------------ forward
     def forward(self, ctx, h, run):
@@ -113,8 +141,15 @@ class DifferentialAttention:
                                kpool if own else None, vpool if own else None, freqs, 2 * H, 2 * G if own else 0,
                                G if own else 0, dim, vdim, 2, rd, page, pages, ctx.err)
         out = ctx.ws.get("attn_out", N, (H * vdim,), ctx.dtype)
-        ops.attention_diff_simple(q, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, G, dim, vdim,
-                                  page, pages, self.chunk, self.scale, self.lam, 1.0 - self.delta, self.eps, ctx.err)
+        if self.uses_mma(ctx):
+            name, n_items = ctx.memo[("diff_tiles", H // G)]
+            ops.attention_diff_mma(q, out, ctx.dev(name), n_items, ctx.dev("q_start"), ctx.dev("q_len"), ctx.dev("pos0"),
+                                   ctx.dev("seq_row"), table, kpool, vpool, H, G, dim, vdim, page, pages, self.chunk,
+                                   self.scale, self.lam, 1.0 - self.delta, self.eps, ctx.err)
+        else:
+            ops.attention_diff_simple(q, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, G, dim,
+                                      vdim, page, pages, self.chunk, self.scale, self.lam, 1.0 - self.delta, self.eps,
+                                      ctx.err)
         y = ctx.ws.get("delta", N, (self.D,), ctx.dtype)
         ops.linear(out, self.wo, out=y)
         return y, None
