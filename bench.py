@@ -636,6 +636,235 @@ def run_kernels(a):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------- another design
+# Layer sizes that resemble real models, for `--design luzosun`: the Luzosun decoder beside the Llama decoder of equal
+# size -- the same width, layers, query and kv heads, q/k/v rows (two maps of `dim` against one head of 2 dim, values of
+# vdim = 2 dim), the same number of feed-forward weights (two matrices of 1.5 F against three of F).
+DESIGN_SIZES = {
+    "1b": dict(width=2048, heads=32, kv_heads=8, dim=32, ff=8192, block=2048),
+    "3b": dict(width=3072, heads=24, kv_heads=8, dim=64, ff=8192, block=4096),
+    "8b": dict(width=4096, heads=32, kv_heads=8, dim=64, ff=14336, block=8192),
+}
+
+
+def design_configs(size, layers, vocab=32000):
+    from mashbox_b200.config.llama import LlamaConfig
+    from mashbox_b200.config.luzosun import LuzosunConfig, LuzosunLayer, LuzosunMixer
+    z = DESIGN_SIZES[size]
+    D, H, KV, dim = z["width"], z["heads"], z["kv_heads"], z["dim"]
+    own = LuzosunMixer(heads=H, kv_heads=KV, dim=dim, vdim=2 * dim, diff=0.3, scale=dim ** -0.5, conv=4,
+                       mask_size=z["block"], rot_base=20000.0, rot_dims=dim // 2, rot_factor=4.0)
+    import dataclasses
+    lz = LuzosunConfig("Luzosun", width=D, vocab=vocab, embedding_scale=1.0, norm_eps=1e-6, canon_taps=4, layers=tuple(
+        LuzosunLayer("attention", own if i % 2 == 0 else dataclasses.replace(own, kv_from=i - 1), z["ff"] * 3 // 2)
+        for i in range(layers)))
+    ll = LlamaConfig(architecture="LlamaForCausalLM", num_layers=layers, hidden=D, num_heads=H, num_kv_heads=KV,
+                     head_dim=2 * dim, intermediate=z["ff"], vocab=vocab, rms_eps=1e-6, rope_theta=20000.0,
+                     rope_scaling=None, tie_embeddings=False, attention_bias=True, max_position=131072)
+    return lz, ll
+
+
+def run_design(a):
+    """`--design luzosun --size 1b|3b|8b`: prefill and decode throughput of the Luzosun decoder and of the Llama decoder
+    of equal size through the step function (random bf16 weights, `--layers` layers, default 4), and the kernels that
+    differ between the two timed alone with their bytes or FLOPs against the measured peaks.  One JSON line."""
+    import numpy as np
+    import torch
+    from mashbox_b200 import ops
+    from mashbox_b200.config.registry import architecture
+    from mashbox_b200.engine.engine import Engine
+    from mashbox_b200.weights.random_init import RandomSource
+    torch.cuda.set_device(0)
+    dev = "cuda:0"
+    layers = a.layers or 4
+    z = DESIGN_SIZES[a.size]
+    cfgs = dict(zip(("luzosun", "llama"), design_configs(a.size, layers)))
+    K, W, B = a.steps, max(3, a.warmup), a.batch
+    ctx = min(a.context, z["block"])            # a Luzosun query reads its block of positions: both read `ctx` keys
+    P = a.prefill_tokens
+    pk = peaks()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    gen = torch.Generator().manual_seed(1)
+    clocks = Clocks()
+    clocks.start()
+    out = {}
+    for name, cfg in cfgs.items():
+        rand_ids = lambda n: torch.randint(0, cfg.vocab, (n,), generator=gen).tolist()
+        per_request = -(-(ctx + 64) // 64) * 64
+        shapes = architecture(cfg.architecture).stored_tensors(cfg)
+        eng = Engine.from_config(cfg, RandomSource(shapes, 0, torch.bfloat16, dev), dtype="bfloat16", device=dev,
+                                 page_size=16, max_tokens=B * per_request + max(P, 2048) + 64, max_requests=B + 1,
+                                 max_tokens_per_step=max(P, 2048) + B, chunk=max(P, 2048), max_context=max(per_request, P + 64),
+                                 cuda_graphs=not a.no_graphs, options=json.loads(a.options) if a.options else None)
+        runner, cache = eng.runner, eng.runner.cache
+        ms = []
+        for i in range(W + 3):                  # a whole prompt of P tokens in one step
+            cache.admit("p")
+            ids = rand_ids(P)
+            torch.cuda.synchronize()
+            e0, e1 = ev(), ev()
+            e0.record()
+            runner.step([("p", ids, [P - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            cache.release("p")
+            if i >= W:
+                ms.append(e0.elapsed_time(e1))
+        pre = statistics.median(ms)
+        rids = [f"d{i}" for i in range(B)]      # B requests of ctx - K - W tokens, then single tokens
+        for r in rids:
+            cache.admit(r)
+            n = ctx - K - W - 1
+            for lo in range(0, n, 2048):
+                runner.step([(r, rand_ids(min(2048, n - lo)), [])])
+        toks = rand_ids(B)
+        step = lambda: runner.step([(r, [t], [0]) for r, t in zip(rids, toks)])
+        for _ in range(W):
+            step()
+        torch.cuda.synchronize()
+        l0 = ops.COUNTERS["launches"]
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(K):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        dec = e0.elapsed_time(e1) / K
+        runner.check()
+        out[name] = {"prefill_tokens_per_s": P / (pre / 1e3), "prefill_ms": pre, "decode_tokens_per_s": B / (dec / 1e3),
+                     "decode_ms_per_step": dec, "decode_launches_per_step": (ops.COUNTERS["launches"] - l0) / K,
+                     "weights_bytes": sum(int(np.prod(sh)) for sh, _ in shapes.values()) * 2}
+        for r in rids:
+            cache.release(r)
+        del eng, runner, cache
+        torch.cuda.empty_cache()
+    out["kernels"] = design_kernels(a, z, P, B, ctx, pk)
+    out["ratio_luzosun_to_llama"] = {k: out["luzosun"][k] / out["llama"][k] for k in ("prefill_tokens_per_s", "decode_tokens_per_s")}
+    print(json.dumps({"impl": "ours", "design": "luzosun", "size": a.size, "layers": layers, "prefill_tokens": P, "batch": B,
+                      "context": ctx, "dtype": "bf16", "data": "synthetic", "peaks": pk, "clocks": clocks.stop(), **out}))
+    return 0
+
+
+def design_kernels(a, z, P, B, ctx, pk):
+    """The kernels of the Luzosun decoder that the Llama decoder has a like kernel for, each pair on the same sizes:
+    CUDA-event time of single launches after an L2 flush, and the fraction of the measured peak (copy bandwidth for
+    the memory-bound ones, bf16 tensor throughput for prompt attention) that the algorithmic bytes or FLOPs come to."""
+    import torch
+    from mashbox_b200 import ops
+    from mashbox_b200.parts.diff_attention import plan_diff_attention
+    dev = "cuda:0"
+    D, H, KV, dim, page = z["width"], z["heads"], z["kv_heads"], z["dim"], 16
+    HD, vd, G, F = 2 * dim, 2 * dim, H // KV, z["ff"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+    bf = lambda *s: (torch.randn(*s, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    err = ops.new_error_word(dev)
+
+    def timed(f):
+        for _ in range(3):
+            f()
+        ts = []
+        for _ in range(max(5, a.steps // 4)):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(ts)
+
+    mem = lambda us, nbytes: {"us": us, "gbs": nbytes / us / 1e3, "frac_of_copy_peak": nbytes / us / 1e3 / pk["hbm_gbs"]}
+    res = {}
+    for form, N, S, klen in (("prompt", P, 1, P), ("decode", B, B, ctx)):
+        pages = S * -(-klen // page)
+        table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(S, -1)
+        kz, vz = bf(pages, KV, page, 2 * dim), bf(pages, KV, page, vd)
+        kl, vl = bf(pages, KV, page, HD), bf(pages, KV, page, HD)
+        q, o = bf(N, H * HD), torch.empty(N, H * HD, device=dev, dtype=torch.bfloat16)
+        q_len = [N // S] * S
+        pos0 = [klen - n for n in q_len]
+        q_start = [i * (N // S) for i in range(S)]
+        seqs = (i32(q_start), i32(q_len), i32(pos0))
+        rows = i32(list(range(S)))
+        plan = {k: i32(v or [0]) for k, v in plan_diff_attention(q_len, pos0, G, KV, z["block"], ops.attention_diff_mma_rows()).items()}
+        tail = (*seqs, rows, table, kz, vz, H, KV, dim, vd, page, pages, z["block"], dim ** -0.5, 0.4, 0.7, 1e-6, err)
+        if form == "prompt":
+            us = timed(lambda: ops.attention_diff_mma(q, o, plan["pre"], plan["pre"].numel() // 2, *tail))
+            if ops.attention_tc5_diff_supports(dim, vd, page):      # what the mixer runs at these sizes
+                res["attention_prompt_luzosun_mma_sync"] = {"us": us}
+                quads = i32(plan_diff_attention(q_len, pos0, G, KV, z["block"], ops.attention_tc5_diff_rows(), quads=True)["pre"])
+                us = timed(lambda: ops.attention_tc5_diff(q, o, quads, quads.numel() // 4, *tail))
+        else:
+            n_slots = plan["slots"].numel() // 2
+            n_part = max(1, n_slots * KV * ops.DIFF_MAX_SPLITS * 2 * ops.DIFF_DECODE_ROWS)
+            po, pm = torch.empty(n_part, vd, device=dev), torch.empty(n_part, 2, device=dev)
+            us = timed(lambda: ops.attention_diff_mma_decode(q, o, plan["dec"], plan["dec"].numel() // 4, plan["slots"],
+                                                             n_slots, po, pm, *tail))
+        if form == "prompt":
+            pairs = P * (P + 1) // 2
+            fz, fl = H * pairs * (2 * 2 * dim * 2 + 2 * 2 * vd), H * pairs * 4 * HD       # two maps: scores of 2 dim, values twice
+            res["attention_prompt_luzosun"] = {"us": us, "tflops": fz / us / 1e6, "frac_of_bf16_peak": fz / us / 1e6 / pk["bf16_tflops"]}
+            rws = ops.attention_tc5_rows() if ops.attention_tc5_supports(HD, page) else 64
+            it = i32([v for m in range(-(-P * G // rws) - 1, -1, -1) for v in (0, m, 0, 1)])
+            if ops.attention_tc5_supports(HD, page):
+                ul = timed(lambda: ops.attention_tc5(q, H * HD, o, kl, vl, it, it.numel() // 4, *seqs, rows, table, H, KV, HD,
+                                                     page, pages, None, HD ** -0.5, err))
+            else:
+                ul = timed(lambda: ops.attention_tma(q, H * HD, o, kl, vl, it, it.numel() // 4, False, *seqs, i32([-1]), rows,
+                                                     table, None, None, 1, H, KV, HD, page, pages, None, HD ** -0.5, err))
+            res["attention_prompt_llama"] = {"us": ul, "tflops": fl / ul / 1e6, "frac_of_bf16_peak": fl / ul / 1e6 / pk["bf16_tflops"]}
+        else:
+            nbytes = B * ctx * KV * (2 * dim + vd) * 2
+            res["attention_decode_luzosun"] = mem(us, nbytes)
+            ns = max(1, min(32, -(-296 // (B * KV)), ctx // 128))
+            ns = 1 << (ns.bit_length() - 1)
+            it = i32([v for s in range(B) for sp in range(ns) for v in (s, 0, sp, ns)])
+            po, pm = torch.empty(B * H * ns, HD, device=dev), torch.empty(B * H * ns, 2, device=dev)
+            ul = timed(lambda: ops.attention_tma(q, H * HD, o, kl, vl, it, B * ns, True, *seqs, rows, rows, table, po, pm, ns,
+                                                 H, KV, HD, page, pages, None, HD ** -0.5, err, merge=ns > 1))
+            res["attention_decode_llama"] = mem(ul, B * ctx * KV * 2 * HD * 2)
+        # what follows the q/k/v product: bias, short convolutions, rotation, cache write / bias, rotation, cache write
+        C = (H + 2 * KV) * HD
+        qkv, qo = bf(N, C), torch.empty(N, H * HD, device=dev, dtype=torch.bfloat16)
+        bias, wc = torch.randn(C, device=dev), torch.randn(4, C, device=dev)
+        state = torch.zeros(S + 1, 3 * C, device=dev)
+        fr = torch.rand(dim // 4, device=dev)
+        positions = i32([p + t for p, n in zip(pos0, q_len) for t in range(n)])
+        tok_row = i32([s for s, n in enumerate(q_len) for _ in range(n)])
+        seq4 = (tok_row, i32(q_start), i32(q_len), rows)
+        us = timed(lambda: ops.conv_rope_kv_write(qkv, bias, wc, state, seq4, positions, tok_row, table, qo, kz, vz, fr,
+                                                  2 * H, 2 * KV, KV, dim, vd, 2, dim // 2, page, pages, err))
+        fl2 = torch.rand(HD // 2, device=dev)
+        ul = timed(lambda: ops.rope_kv_write(qkv, bias, positions, tok_row, table, kl, vl, fl2, H, KV, HD, HD, 1, page,
+                                             pages, err))
+        res[f"after_qkv_{form}_luzosun"] = mem(us, N * C * 2 * 2)
+        res[f"after_qkv_{form}_llama"] = mem(ul, N * C * 2 * 2)
+        # the norms: one kernel makes both of a Luzosun layer (x, two deltas, two outputs) / one norm (x, delta, output)
+        x = torch.randn(N, D, device=dev)
+        d1, d2, o1, o2 = bf(N, D), bf(N, D), bf(N, D), bf(N, D)
+        w1 = torch.ones(D, device=dev)
+        us = timed(lambda: ops.add_rmsnorm_pair(x, d1, d2, w1, w1, 1e-6, o1, o2))
+        ul = timed(lambda: ops.add_rmsnorm(x, d1, None, w1, 1e-6, o1))
+        res[f"norms_{form}_luzosun"] = mem(us, N * D * (4 + 4 + 4 * 2))
+        res[f"norm_{form}_llama"] = mem(ul, N * D * (4 + 4 + 2 * 2))
+        st2 = torch.zeros(S + 1, 3 * D, device=dev)
+        wd = torch.randn(4, D, device=dev)
+        us = timed(lambda: ops.short_conv(d1, wd, st2, seq4, o1, True))
+        res[f"input_conv_{form}_luzosun"] = mem(us, N * D * 2 * 2)
+        # the activation between the feed-forward's products
+        up, act = bf(N, F * 3 // 2), torch.empty(N, F * 3 // 2, device=dev, dtype=torch.bfloat16)
+        gu, ga = bf(N, 2 * F), torch.empty(N, F, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda: ops.xielu(up, act, 0.8, 1.2))
+        ul = timed(lambda: ops.swiglu(gu, ga))
+        res[f"activation_{form}_luzosun"] = mem(us, N * (F * 3 // 2) * 2 * 2)
+        res[f"activation_{form}_llama"] = mem(ul, N * F * 3 * 2)
+        del kz, vz, kl, vl
+    ops.check_error_word(err)
+    return res
+
+
 def run_reference(a):
     """The reference arm: mashbox's own engine from baseline/_ref.  mashbox 0.1.15 installs there with --no-deps, but
     its model and engine modules import JAX (not in this image, no network) and it runs on TPU chips."""
@@ -680,6 +909,9 @@ def main():
     ap.add_argument("--requests", type=int, default=0, help="workloads: fewer requests than the workload names")
     ap.add_argument("--pool-tokens", type=int, default=0, help="workloads: size of the cache pool (0: every request fits)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--design", default="", choices=("", "luzosun"),
+                    help="another design beside the Llama decoder of equal size (prefill, decode, single kernels)")
+    ap.add_argument("--size", default="8b", choices=tuple(DESIGN_SIZES), help="--design: the layer sizes")
     ap.add_argument("--workload-warm", type=int, default=1, help="workloads: run the workload once untimed first")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -691,6 +923,8 @@ def main():
     a.warmup = max(a.warmup, 3)
     if a.workload:
         return run_workload(a)
+    if a.design:
+        return run_design(a)
     if a.attention:
         return run_attention(a)
     if a.timeline:

@@ -25,7 +25,17 @@
 
 #define T5_BM 128                              // rows of one query tile: one softmax warpgroup, thread = row
 #define T5_QT 2                                // query tiles of a block, sharing the K and V tiles
+// Compiled with -DT5_DIFF the kernel is the DIFFERENTIAL form: a head has two attention maps, [map 0 | map 1] side by side
+// in a query row and in a key row (HD / 2 each), over one set of values of HD.  The two "query tiles" of a unit are then
+// the two maps of the SAME 128 rows: the score product of map g runs over map g's half of the k-steps, both output
+// products read the one value tile, and at the end the warpgroup of map 1 hands its rows' 1 / sum over and the
+// warpgroup of map 0 reads both accumulators and writes (a_0 - lam a_1) / rms * gain.  `window` is the size of the block
+// of positions a query sees (blocks counted from position 0; 0: every earlier key) instead of a sliding window.
+#ifdef T5_DIFF
+#define T5_ROWS T5_BM
+#else
 #define T5_ROWS (T5_BM * T5_QT)
+#endif
 #define T5_THREADS (T5_QT * T5_BM + 128)       // two softmax warpgroups; a third holds the producer warp and the product warp
 #define T5_BN 128
 #define T5_HALF (128 * 128)                    // bytes of 128 rows of 64 bf16: what one 128-byte-swizzled column half of a tile takes
@@ -118,11 +128,18 @@ __device__ __forceinline__ bool t5_unit(const AttnParams& P, int unit, T5Unit& U
     U.row0 = item.y * T5_ROWS;
     if (U.row0 >= U.R) return false;
     const int pos_min = U.pos0 + U.row0 / U.G;
+#ifdef T5_DIFF
+    U.lo = P.window > 0 ? pos_min / P.window * P.window : 0;
+#else
     U.lo = (P.window > 0 && pos_min - P.window + 1 > 0) ? pos_min - P.window + 1 : 0;
+#endif
     U.lo_al = (U.lo / T5_BN) * T5_BN;
     U.pmin0 = pos_min;
     U.pmax0 = U.pos0 + (min(U.R, U.row0 + T5_BM) - 1) / U.G;
     U.T0 = (U.pmax0 + 1 - U.lo_al + T5_BN - 1) / T5_BN;             // at least one
+#ifdef T5_DIFF
+    U.pmin1 = U.pmin0; U.pmax1 = U.pmax0; U.T1 = U.T0;             // the second tile is the second map of the same rows
+#else
     const int r1 = U.row0 + T5_BM;
     if (r1 < U.R) {
         U.pmin1 = U.pos0 + r1 / U.G;
@@ -132,6 +149,7 @@ __device__ __forceinline__ bool t5_unit(const AttnParams& P, int unit, T5Unit& U
         U.pmin1 = U.pmax1 = 0;
         U.T1 = 0;
     }
+#endif
     U.T = max(U.T0, U.T1);
     U.hi = max(U.pmax0, U.pmax1) + 1;
     U.tb = P.table + (size_t)P.seq_row[seq] * P.max_blocks;
@@ -158,9 +176,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
     // 2 x Q tile | 2 stages x K tile | 2 stages x V tile (32 KB each at head size 128, 16 KB at 64) | barriers
     const uint32_t q_s0 = smem_u32(smem), k_s0 = q_s0 + T5_QT * TILE, v_s0 = k_s0 + 2 * TILE;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T5_QT * TILE + 4 * TILE);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    float* meet = reinterpret_cast<float*>(bars + 22);             // differential form: 1 / sum of the rows of map 1
     const uint32_t k_full0 = smem_u32(bars), k_empty0 = k_full0 + 16, v_full0 = k_full0 + 32, v_empty0 = k_full0 + 48,
-                   s_full0 = k_full0 + 64, p_full0 = k_full0 + 80, o_done0 = k_full0 + 96, q_ready0 = k_full0 + 112;
+                   s_full0 = k_full0 + 64, p_full0 = k_full0 + 80, o_done0 = k_full0 + 96, q_ready0 = k_full0 + 112,
+                   a1_ready = k_full0 + 128, o1_read = k_full0 + 136;       // differential form: map 1 handed over / read
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 8 * 32) {
@@ -180,6 +200,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
             mbar_init(v_empty0 + 8 * s, 1); mbar_init(s_full0 + 8 * s, 1); mbar_init(p_full0 + 8 * s, T5_BM);
             mbar_init(o_done0 + 8 * s, 1); mbar_init(q_ready0 + 8 * s, T5_BM);
         }
+        mbar_init(a1_ready, T5_BM); mbar_init(o1_read, T5_BM);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
@@ -270,11 +291,16 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                     if (!mbar_wait(k_full0 + 8 * s, (n >> 1) & 1, P.err)) return false;
                     tc_fence_after();
                     const uint32_t k_lo = umma_desc_lo(k_s0 + s * TILE, 0), q_lo = umma_desc_lo(q_s0 + g * TILE, 0);
+#ifdef T5_DIFF
+                    const int ks0 = g * (HD / 32), ks1 = ks0 + HD / 32;                   // map g's half of the row
+#else
+                    const int ks0 = 0, ks1 = HD / 16;
+#endif
 #pragma unroll
-                    for (int ks = 0; ks < HD / 16; ks++) {
+                    for (int ks = ks0; ks < ks1; ks++) {
                         constexpr uint32_t half = T5_HALF >> 4;
                         const uint32_t off = (ks >> 2) * half + (ks & 3) * 2;             // in 16-byte units
-                        umma_f16(tm_s0 + g * 128, umma_desc_join(q_lo + off), umma_desc_join(k_lo + off), idesc_qk, ks > 0);
+                        umma_f16(tm_s0 + g * 128, umma_desc_join(q_lo + off), umma_desc_join(k_lo + off), idesc_qk, ks > ks0);
                     }
                     if (last_reader(g, t)) umma_commit(k_empty0 + 8 * s);
                     umma_commit(s_full0 + 8 * g);
@@ -334,7 +360,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
         };
         // the unit's query tile goes into shared memory (asynchronous copies, waited for in publish_q)
         auto fetch_q = [&]() {
+#ifdef T5_DIFF
+            const int row_g = U.row0;
+#else
             const int row_g = U.row0 + g * T5_BM;
+#endif
             for (int cid = st; cid < T5_BM * (HD / 8); cid += T5_BM) {
                 const int row = cid / (HD / 8), c = cid % (HD / 8), rr = row_g + row;
                 const bf16* src = P.q;
@@ -357,12 +387,20 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
         if (unit >= 0) { fetch_q(); publish_q(); }
         while (ok && unit >= 0) {
             const int Tq = U.tiles(g), pos_min_g = U.pmin(g), pos_max_g = U.pmax(g);
+#ifdef T5_DIFF
+            const int G = U.G, R = U.R, r = U.row0 + r_loc;
+#else
             const int G = U.G, R = U.R, r = U.row0 + g * T5_BM + r_loc;
+#endif
             const int tok0 = U.tok0, kvh = U.kvh, lo_al = U.lo_al, pos0 = U.pos0;
             int rpos = -1, rlo = 0;
             if (r < R) {
                 rpos = pos0 + r / G;
+#ifdef T5_DIFF
+                rlo = P.window > 0 ? rpos / P.window * P.window : 0;
+#else
                 rlo = (P.window > 0 && rpos - P.window + 1 > 0) ? rpos - P.window + 1 : 0;
+#endif
             }
             float m_run = -INFINITY, l_run = 0.0f;
             for (int t = 0; t < Tq && ok; t++) {
@@ -371,7 +409,13 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                 if (!mbar_wait(s_full0 + 8 * g, (nt + t) & 1, P.err)) { ok = false; break; }
                 tc_fence_after();
                 const int kb = lo_al + t * T5_BN;
+#ifdef T5_DIFF
+                // every key of the tile lies at or before the first row and in the block of positions of the last row
+                // (and so of every row between)
+                const bool full_tile = kb + T5_BN - 1 <= pos_min_g && kb >= ((P.window > 0) ? pos_max_g / P.window * P.window : 0);
+#else
                 const bool full_tile = kb + T5_BN - 1 <= pos_min_g && kb >= ((P.window > 0) ? pos_max_g - P.window + 1 : 0);
+#endif
                 // the row's 128 scores come from tensor memory with four loads and ONE wait (a load and its wait are a
                 // round trip of several hundred cycles) and stay in registers for both passes
                 uint32_t sv[4][32];
@@ -474,6 +518,63 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
             if (!mbar_wait(o_done0 + 8 * g, nu & 1, P.err)) { ok = false; break; }
             tc_fence_after();
             if (unit >= 0) publish_q();
+#ifdef T5_DIFF
+            {
+                const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+                if (g == 1) {
+                    // map 1: its accumulator is complete; hand the rows' 1 / sum over and wait until map 0's warpgroup
+                    // has read the accumulator, which the next unit's first output product overwrites
+                    meet[r_loc] = inv;
+                    mbar_arrive(a1_ready);
+                    if (!mbar_wait(o1_read, nu & 1, P.err)) { ok = false; break; }
+                } else {
+                    if (!mbar_wait(a1_ready, nu & 1, P.err)) { ok = false; break; }
+                    tc_fence_after();
+                    const float inv1 = meet[r_loc] * P.diff_lam;
+                    const uint32_t o1_addr = tm_o0 + HD + lane_addr;
+                    const bool live_row = r < R;
+                    float ss = 0.0f;
+#pragma unroll 1
+                    for (int c = 0; c < OC; c++) {                  // first pass: the row's sum of squares
+                        uint32_t a[32], b[32];
+                        tmem_ld32(o_addr + c * 32, a);
+                        tmem_ld32(o1_addr + c * 32, b);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            const float o = __uint_as_float(a[i]) * inv - __uint_as_float(b[i]) * inv1;
+                            ss = fmaf(o, o, ss);
+                        }
+                    }
+                    const float f = rsqrtf(ss / (float)HD + P.diff_eps) * P.diff_gain;
+                    const float f0 = inv * f, f1 = inv1 * f;
+                    bf16* dst = P.out + (live_row ? ((size_t)(tok0 + r / G) * P.H + (kvh * G + r % G)) * HD : 0);
+#pragma unroll 1
+                    for (int c = 0; c < OC; c++) {                  // second pass: the row itself
+                        uint32_t a[32], b[32];
+                        tmem_ld32(o_addr + c * 32, a);
+                        tmem_ld32(o1_addr + c * 32, b);
+                        tmem_ld_wait();
+                        if (c == OC - 1) {
+                            tc_fence_before();
+                            mbar_arrive(o1_read);                   // map 1's accumulator may be overwritten now
+                        }
+                        if (live_row) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 16) {
+                                uint32_t w[8];
+#pragma unroll
+                                for (int e = 0; e < 8; e++)
+                                    w[e] = pack_bf16(__uint_as_float(a[i + 2 * e]) * f0 - __uint_as_float(b[i + 2 * e]) * f1,
+                                                     __uint_as_float(a[i + 2 * e + 1]) * f0 - __uint_as_float(b[i + 2 * e + 1]) * f1);
+                                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"l"(dst + c * 32 + i),
+                                             "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                            }
+                        }
+                    }
+                }
+            }
+#else
             {
                 const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
                 const bool live_row = r < R;                        // rows past the end take part in the loads only
@@ -496,6 +597,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                     }
                 }
             }
+#endif
             nu++;
             nt += Tq;
         }
@@ -545,7 +647,7 @@ MB_API int mb_attn_tc5_supports(int HD, int page) {
 
 template <int HD>
 static int launch_tc5(const AttnParams& P, const CUtensorMap& kmap, const CUtensorMap& vmap, int n_units, cudaStream_t st) {
-    constexpr size_t smem = 1024 + (T5_QT + 4) * (size_t)(T5_BN * HD * 2) + 16 * 8 + 16;
+    constexpr size_t smem = 1024 + (T5_QT + 4) * (size_t)(T5_BN * HD * 2) + 22 * 8 + T5_BM * 4;
     static bool configured = false;
     static int sms = 0;
     if (!configured) {
@@ -562,14 +664,26 @@ static int launch_tc5(const AttnParams& P, const CUtensorMap& kmap, const CUtens
     return 0;
 }
 
-// items: (sequence, tile of T5_ROWS = 256 packed rows, 0, 1), heaviest first -- this kernel does not split the keys over blocks.
-MB_API int mb_attn_tc5_bf16(const void* q, int q_stride, void* out, const void* kpool, const void* vpool,
+// items: (sequence, tile of T5_ROWS packed rows, 0, 1), heaviest first -- this kernel does not split the keys over blocks.
+#ifdef T5_DIFF
+#define T5_ENTRY mb_attn_tc5_diff_bf16
+#else
+#define T5_ENTRY mb_attn_tc5_bf16
+#endif
+MB_API int T5_ENTRY(const void* q, int q_stride, void* out, const void* kpool, const void* vpool,
                             const void* items, int n_items, const int* q_start, const int* q_len, const int* pos0,
                             const int* seq_row, const int* table, int max_blocks, int H, int KV, int HD, int page,
-                            int num_pages, int window, float scale, int* err, cudaStream_t st) {
+                            int num_pages, int window, float scale,
+#ifdef T5_DIFF
+                            float lam, float gain, float eps,
+#endif
+                            int* err, cudaStream_t st) {
     if (n_items == 0) return 0;
     if (!mb_attn_tc5_supports(HD, page) || KV < 1 || H % KV || KV > 65535) return -2;
     AttnParams P;
+#ifdef T5_DIFF
+    P.diff_lam = lam; P.diff_gain = gain; P.diff_eps = eps;
+#endif
     P.q = (const bf16*)q; P.q_stride = q_stride; P.out = (bf16*)out;
     P.kpool = (const bf16*)kpool; P.vpool = (const bf16*)vpool;
     P.items = (const int4*)items;

@@ -186,17 +186,19 @@ def xielu(z, out, ap, an):
 
 # ------------------------------------------------------------------------------------------------ short convolutions
 def short_conv(x, w, state, seq, out, residual=False):
-    """out = (x if residual) + causal_conv(x): x, out (N, C) in the activation dtype, w (C, taps) float32, one filter per
-    channel.  state (slots, taps - 1, C) float32 (a view: rows C apart, slots state.stride(0) apart) holds every
+    """out = (x if residual) + causal_conv(x): x, out (N, C) in the activation dtype, w (taps, C) float32, one filter per
+    channel, held tap by tap (the transpose of how checkpoints store them).  state (slots, taps - 1, C) float32 (a view: rows C apart, slots state.stride(0) apart) holds every
     sequence's last taps - 1 inputs and is replaced by this step's.  seq = (tok_seq, q_start, q_len, state_slot) int32
     device arrays: per token its sequence's index in the step; per sequence its first token, length and state slot."""
     _cuda(x, w, state, out, *seq)
     N, C = x.shape
-    taps = w.shape[1]
+    taps = w.shape[0]
+    if w.shape[1] != C or not w.is_contiguous():
+        raise KernelError("short_conv: the filters must be a contiguous (taps, channels) tensor")
     f = _fn("short_conv", "mb_short_conv_" + _suffix(x.dtype),
-            [c_void_p, c_void_p, c_void_p, ctypes.c_longlong] + [c_void_p] * 5 + [c_int] * 4 + [c_void_p])
-    _check(f(_p(x), _p(w), _p(state), state.stride(0) if state is not None else 0, *[_p(t) for t in seq], _p(out), N, C,
-             taps, 1 if residual else 0, _stream()), "short_conv")
+            [c_void_p, c_void_p, c_void_p, ctypes.c_longlong] + [c_void_p] * 5 + [c_int] * 5 + [c_void_p])
+    _check(f(_p(x), _p(w), _p(state), state.stride(0) if state is not None else 0, *[_p(t) for t in seq], _p(out), N,
+             seq[1].shape[0], C, taps, 1 if residual else 0, _stream()), "short_conv")
 
 
 def conv_rope_kv_write(qkv, bias, w, state, seq, positions, tok_row, table, q_out, kpool, vpool, freqs, QU, KU, VH, dim,
@@ -209,13 +211,16 @@ def conv_rope_kv_write(qkv, bias, w, state, seq, positions, tok_row, table, q_ou
     head, vpool (pages, VH, page, vdim).  KU = VH = 0: the rows hold queries only."""
     _cuda(qkv, bias, w, state, positions, tok_row, table, q_out, kpool, vpool, freqs, *seq)
     N = qkv.shape[0]
-    taps = 1 if w is None else w.shape[1]
+    taps = 1 if w is None else w.shape[0]
+    if w is not None and (w.shape[1] != qkv.shape[1] or not w.is_contiguous()):
+        raise KernelError("conv_rope_kv_write: the filters must be a contiguous (taps, channels) tensor")
     f = _fn("short_conv", "mb_conv_rope_kv_write_" + _suffix(qkv.dtype),
             [c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong] + [c_void_p] * 7 + [c_int] + [c_void_p] * 4
-            + [c_int] * 11 + [c_void_p, c_void_p])
+            + [c_int] * 12 + [c_void_p, c_void_p])
     _check(f(_p(qkv), _p(bias), _p(w), _p(state), state.stride(0) if state is not None else 0, *[_p(t) for t in seq],
              _p(positions), _p(tok_row), _p(table), table.shape[1] if table is not None else 0, _p(q_out), _p(kpool),
-             _p(vpool), _p(freqs), N, QU, KU, VH, dim, vdim, kper, RD, page, num_pages, taps, _p(err), _stream()),
+             _p(vpool), _p(freqs), N, seq[1].shape[0], QU, KU, VH, dim, vdim, kper, RD, page, num_pages, taps, _p(err),
+             _stream()),
            "conv_rope_kv_write")
 
 
@@ -571,6 +576,30 @@ def attention_diff_mma_rows():
     return DIFF_MMA_ROWS
 
 
+DIFF_DECODE_ROWS, DIFF_MAX_SPLITS = 16, 16
+
+
+def attention_diff_mma_decode(q, out, items, n_items, slots, n_slots, part_o, part_ml, q_start, q_len, pos0, seq_row, table,
+                              kpool, vpool, H, G, dim, vdim, page, num_pages, chunk, scale, lam, gain, eps, err):
+    """The decode form of attention_diff_mma, for sequences of at most 16 packed rows: items are n_items (sequence,
+    split, number of splits, slot) quadruples, the keys of a sequence cut into splits that run side by side; slots:
+    n_slots (sequence, number of splits) pairs of the sequences that are cut, whose splits a second kernel merges from
+    part_o (n_slots * G * 16 * 2 * 16, vdim) and part_ml (the same rows, 2), float32."""
+    _cuda(q, out, items, slots, part_o, part_ml, q_start, q_len, pos0, seq_row, table, kpool, vpool)
+    if q.dtype != torch.bfloat16 or not attention_diff_mma_supports(dim, vdim):
+        raise KernelError(f"attention_diff_mma_decode: no kernel for {q.dtype} with head sizes {dim} and {vdim}")
+    from .build import variant
+    lib = variant(f"attention_diff_mma_{dim}_{vdim}", "attention_diff_mma.cu", [f"-DDIFF_DIM={dim}", f"-DDIFF_VD={vdim}"])
+    f = _fn(lib, "mb_attn_diff_mma_decode", [c_void_p] * 5 + [c_int, c_void_p, c_int] + [c_void_p] * 7 + [c_int] * 6
+            + [c_float] * 4 + [c_void_p, c_void_p])
+    _check(f(_p(q), _p(out), _p(kpool), _p(vpool), _p(items), int(n_items), _p(slots), int(n_slots), _p(part_o),
+             _p(part_ml), _p(q_start), _p(q_len), _p(pos0), _p(seq_row), _p(table), table.shape[1], H, G, page, num_pages,
+             int(chunk or 0), float(scale), float(lam), float(gain), float(eps), _p(err), _stream()),
+           "attention_diff_mma_decode")
+    if n_slots:
+        COUNTERS["launches"] += 1
+
+
 def attention_diff_mma(q, out, items, n_items, q_start, q_len, pos0, seq_row, table, kpool, vpool, H, G, dim, vdim, page,
                        num_pages, chunk, scale, lam, gain, eps, err):
     """Differential attention on tensor cores (bfloat16): the same result as attention_diff_simple.  items: n_items
@@ -737,6 +766,31 @@ def attention_tc5(q, q_stride, out, kpool, vpool, items, n_items, q_start, q_len
     _check(f(_p(q), q_stride, _p(out), _p(kpool), _p(vpool), _p(items), n_items, _p(q_start), _p(q_len), _p(pos0),
              _p(seq_row), _p(table), table.shape[1], H, KV, HD, page, num_pages, window or 0, float(scale),
              _p(err), _stream()), "attention_tc5")
+
+
+def attention_tc5_diff_supports(dim, vdim, page):
+    """the tcgen05 kernel's differential form: two maps of `dim` side by side are one row of vdim = 2 dim = 64 or 128"""
+    return 2 * dim == vdim and attention_tc5_supports(vdim, page)
+
+
+def attention_tc5_diff_rows():
+    """packed query rows of one work item of the differential form (both maps of 128 rows)"""
+    return 128
+
+
+def attention_tc5_diff(q, out, items, n_items, q_start, q_len, pos0, seq_row, table, kpool, vpool, H, G, dim, vdim, page,
+                       num_pages, chunk, scale, lam, gain, eps, err):
+    """Prompt-form differential attention on tcgen05 (the result of attention_diff_simple): items are (sequence, tile of
+    128 packed rows, 0, 1); q (N, H * 2 dim), kpool (pages, G, page, 2 dim), vpool (pages, G, page, vdim), vdim = 2 dim."""
+    _cuda(q, out, kpool, vpool, items, q_start, q_len, pos0, seq_row, table)
+    if q.dtype != torch.bfloat16 or not attention_tc5_diff_supports(dim, vdim, page):
+        raise KernelError(f"attention_tc5_diff: no kernel for {q.dtype}, head sizes {dim} and {vdim}, pages of {page}")
+    f = _fn("attention_tc5_diff", "mb_attn_tc5_diff_bf16",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int] + [c_int] * 6 + [c_float] * 4 + [c_void_p, c_void_p])
+    _check(f(_p(q), H * vdim, _p(out), _p(kpool), _p(vpool), _p(items), n_items, _p(q_start), _p(q_len), _p(pos0),
+             _p(seq_row), _p(table), table.shape[1], H, G, vdim, page, num_pages, int(chunk or 0), float(scale), float(lam),
+             float(gain), float(eps), _p(err), _stream()), "attention_tc5_diff")
 
 
 def attention_merge(part_o, part_ml, part_tok, n_part, out, H, HD, max_splits):

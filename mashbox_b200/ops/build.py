@@ -39,6 +39,7 @@ LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "attention_mma_wide": ("attention_mma.cu", ["-DMB_ATTN_WIDE"]),    # the other multiples of 16 up to 256
     "attention_tma": ("attention_tma.cu", []),
     "attention_tc5": ("attention_tc5.cu", []),
+    "attention_tc5_diff": ("attention_tc5.cu", ["-DT5_DIFF"]),         # two maps per head over one set of values
     "sampling": ("sampling.cu", []),
     "sampling_noalloc": ("sampling_noalloc.cu", []),
     "trace": ("trace.cu", []),

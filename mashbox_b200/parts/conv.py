@@ -42,7 +42,7 @@ class ShortConv:
         return [Want(self.name, (self.C, self.taps), "vector")]
 
     def bind(self, tensors, env):
-        self.weight = tensors[self.name]
+        self.weight = tensors[self.name].t().contiguous()          # tap by tap, as the kernels read them
 
     def state_floats(self):
         return (self.taps - 1) * self.C

@@ -31,14 +31,42 @@ from .conv import plan_sequences, state_view, step_sequences
 
 
 def plan_diff_tiles(q_len, pos0, group, rows):
-    """Work list of the tensor-core kernel: one (sequence, tile) pair per `rows` packed query rows -- a sequence's
-    tokens times the `group` query heads of a kv head -- the tiles that reach the most keys first.  -> flat int list"""
-    items = []
+    """Work list of the prompt form of the tensor-core kernel: one (sequence, tile) pair per `rows` packed query rows --
+    a sequence's tokens times the `group` query heads of a kv head -- the tiles that reach the most keys first.
+    -> flat int list"""
+    return plan_diff_attention(q_len, pos0, group, 1, None, rows, decode_rows=0)["pre"]
+
+
+def plan_diff_attention(q_len, pos0, group, kv_heads, chunk, rows, decode_rows=16, max_splits=16, target=296, splits=None,
+                        quads=False):
+    """The two work lists of the tensor-core kernels of the differential attention, as flat int lists.  "pre": (sequence,
+    tile of `rows` packed rows) for sequences of more than `decode_rows` packed rows (`quads`: as (sequence, tile, 0,
+    1), the form the tcgen05 kernel reads).  "dec": (sequence, split, number
+    of splits, slot) for the others: their keys -- from the start of the block of `chunk` positions the sequence's first
+    query lies in -- are cut into a power of two of splits, as many as fill `target` blocks with the step's decode-form
+    sequences times the kv heads, never fewer than two tiles of 64 keys to a split (`splits`: that many, whatever the
+    sizes).  "slots": (sequence, number of splits) of the sequences that are cut; the kernel that merges the splits runs
+    over these."""
+    pre, dec, slots = [], [], []
+    short = [s for s, n in enumerate(q_len) if n * group <= decode_rows]
+    want = max(1, target // max(1, len(short) * kv_heads))
     for s, n in enumerate(q_len):
-        for m in range(-(-n * group // rows)):
-            items.append((-min(n, (m + 1) * rows // group), s, m))
-    items.sort()
-    return [v for it in items for v in it[1:]]
+        if n * group > decode_rows:
+            for m in range(-(-n * group // rows)):
+                pre.append((-(pos0[s] + min(n, (m + 1) * rows // group)), s, m))
+            continue
+        lo = pos0[s] // chunk * chunk if chunk else 0
+        tiles = -(-(pos0[s] + n - lo // 64 * 64) // 64)
+        ns = max(1, min(max_splits, want, tiles // 2)) if splits is None else max(1, min(max_splits, int(splits)))
+        ns = 1 << (ns.bit_length() - 1)
+        slot = -1
+        if ns > 1:
+            slot = len(slots)
+            slots.append((s, ns))
+        dec += [(s, sp, ns, slot) for sp in range(ns)]
+    pre.sort()
+    flat = lambda items: [v for it in items for v in it]
+    return dict(pre=flat([it[1:] + ((0, 1) if quads else ()) for it in pre]), dec=flat(dec), slots=flat(slots))
 
 
 class DifferentialAttention:
@@ -85,7 +113,7 @@ class DifferentialAttention:
         cat = lambda suffix: torch.cat([tensors[self.n[r] + suffix] for r in self.roles], 0).contiguous()
         self.w = cat("")
         self.b = cat(self.n["bias"]) if self.bias else None
-        self.wconv = cat(self.n["conv"]) if self.taps > 1 else None
+        self.wconv = cat(self.n["conv"]).t().contiguous() if self.taps > 1 else None      # (taps, channels)
         self.wo = tensors[self.n["o"]]
         dot = lambda a, b: float((tensors[self.n[a]].double() * tensors[self.n[b]].double()).sum())
         self.lam = math.exp(dot("lq1", "lk1")) - math.exp(dot("lq2", "lk2")) + self.delta
@@ -116,12 +144,28 @@ class DifferentialAttention:
         plan_sequences(ctx)
         if not self.uses_mma(ctx):
             return
-        key = ("diff_tiles", self.H // self.G)
+        key = self.plan_key()
         if key not in ctx.memo:
-            name = f"diff_tiles_{self.H // self.G}"
-            items = plan_diff_tiles(ctx.q_len, ctx.pos0, self.H // self.G, ctx.ops.attention_diff_mma_rows())
-            ctx.inputs.add(name, np.asarray(items, np.int32))
-            ctx.memo[key] = (name, len(items) // 2)
+            name = "diff%d_" % len([k for k in ctx.memo if k[0] == "diff_attention"])
+            tc5 = self.uses_tc5(ctx)
+            rows = ctx.ops.attention_tc5_diff_rows() if tc5 else ctx.ops.attention_diff_mma_rows()
+            plan = plan_diff_attention(ctx.q_len, ctx.pos0, self.H // self.G, self.G, self.chunk, rows,
+                                       ctx.ops.DIFF_DECODE_ROWS, ctx.ops.DIFF_MAX_SPLITS,
+                                       int(ctx.options.get("attention_target_blocks", 296)),
+                                       ctx.options.get("attention_splits"), quads=tc5)
+            for k, v in plan.items():
+                ctx.inputs.add(name + k, np.asarray(v, np.int32))
+            ctx.memo[key] = dict(name=name, tc5=tc5, n_pre=len(plan["pre"]) // (4 if tc5 else 2),
+                                 n_dec=len(plan["dec"]) // 4, n_slots=len(plan["slots"]) // 2)
+
+    def uses_tc5(self, ctx):
+        """prompt-form tiles go to the tcgen05 kernel when a row of two maps is as wide as a value row of 64 or 128"""
+        return (ctx.options.get("attention_prefill_kernel", "tc5") == "tc5"
+                and ctx.ops.attention_tc5_diff_supports(self.dim, self.vdim, ctx.cache.page_size))
+
+    def plan_key(self):
+        # everything the work lists depend on (the head sizes decide the kernel and its rows per tile)
+        return ("diff_attention", self.H // self.G, self.G, self.chunk, self.dim, self.vdim)
 
     # ------------------------------------------------------------------------------------------ forward
     def forward(self, ctx, h, run):
@@ -142,10 +186,23 @@ class DifferentialAttention:
                                G if own else 0, dim, vdim, 2, rd, page, pages, ctx.err)
         out = ctx.ws.get("attn_out", N, (H * vdim,), ctx.dtype)
         if self.uses_mma(ctx):
-            name, n_items = ctx.memo[("diff_tiles", H // G)]
-            ops.attention_diff_mma(q, out, ctx.dev(name), n_items, ctx.dev("q_start"), ctx.dev("q_len"), ctx.dev("pos0"),
-                                   ctx.dev("seq_row"), table, kpool, vpool, H, G, dim, vdim, page, pages, self.chunk,
-                                   self.scale, self.lam, 1.0 - self.delta, self.eps, ctx.err)
+            import torch
+            plan = ctx.memo[self.plan_key()]
+            nm = plan["name"]
+            seqs = (ctx.dev("q_start"), ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev("seq_row"))
+            tail = (table, kpool, vpool, H, G, dim, vdim, page, pages, self.chunk, self.scale, self.lam, 1.0 - self.delta,
+                    self.eps, ctx.err)
+            if plan["n_pre"]:
+                prompt_form = ops.attention_tc5_diff if plan["tc5"] else ops.attention_diff_mma
+                prompt_form(q, out, ctx.dev(nm + "pre"), plan["n_pre"], *seqs, *tail)
+            if plan["n_dec"]:
+                part_o = part_ml = None
+                if plan["n_slots"]:
+                    n = plan["n_slots"] * G * ops.DIFF_MAX_SPLITS * 2 * ops.DIFF_DECODE_ROWS
+                    part_o = ctx.ws.get("diff_part_o", n, (vdim,), torch.float32, reserve=0)
+                    part_ml = ctx.ws.get("diff_part_ml", n, (2,), torch.float32, reserve=0)
+                ops.attention_diff_mma_decode(q, out, ctx.dev(nm + "dec"), plan["n_dec"], ctx.dev(nm + "slots"),
+                                              plan["n_slots"], part_o, part_ml, *seqs, *tail)
         else:
             ops.attention_diff_simple(q, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, G, dim,
                                       vdim, page, pages, self.chunk, self.scale, self.lam, 1.0 - self.delta, self.eps,

@@ -32,11 +32,12 @@ def seq_arrays(q_lens, slots):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("C", [40, 37])          # eight channels a thread, and the widths that form does not take
 @pytest.mark.parametrize("taps,residual", [(2, True), (4, False), (5, True), (8, False), (1, True)])
-def test_short_conv_carries_its_state_across_any_cut(dtype, taps, residual):
+def test_short_conv_carries_its_state_across_any_cut(dtype, taps, residual, C):
     from mashbox_b200 import ops
     g = torch.Generator().manual_seed(taps)
-    C, T = 40, 37
+    T = 37
     u = [torch.randn(T, C, generator=g).to(TD[dtype]).double() for _ in range(3)]
     w = torch.randn(C, taps, generator=g)
     want = [plain.causal_conv(x, w.double()) + (x if residual else 0) for x in u]
@@ -55,7 +56,7 @@ def test_short_conv_carries_its_state_across_any_cut(dtype, taps, residual):
         lens = [cuts[s][step] for s in live]
         x = torch.cat([u[s][at[s]:at[s] + n] for s, n in zip(live, lens)]).to(DEV, TD[dtype]).contiguous()
         out = torch.empty_like(x)
-        ops.short_conv(x, w.to(DEV), view, seq_arrays(lens, [slots[s] for s in live]), out, residual)
+        ops.short_conv(x, w.t().contiguous().to(DEV), view, seq_arrays(lens, [slots[s] for s in live]), out, residual)
         o = 0
         for s, n in zip(live, lens):
             got[s].append(out[o:o + n])
@@ -146,8 +147,10 @@ class DiffCase:
 
 
 def run_diff(case, chunk, scale, lam, delta, eps, kernel="simple"):
+    """kernel: "simple", "mma" (the plan the mixer makes), "mma-N" (decode-form sequences cut into N splits) or "tc5"
+    (prompt-form sequences on the tcgen05 kernel)"""
     from mashbox_b200 import ops
-    from mashbox_b200.parts.diff_attention import plan_diff_tiles
+    from mashbox_b200.parts.diff_attention import plan_diff_attention
     out = torch.empty(case.N, case.H * case.vdim, device=DEV, dtype=TD[case.dtype])
     err = ops.new_error_word(DEV)
     args = (case.H, case.G, case.dim, case.vdim, case.page, case.pages, chunk, scale, lam, 1.0 - delta, eps, err)
@@ -157,9 +160,22 @@ def run_diff(case, chunk, scale, lam, delta, eps, kernel="simple"):
     else:
         q_start = np.concatenate([[0], np.cumsum(case.q_lens)[:-1]])
         pos0 = [n - q for n, q in zip(case.lengths, case.q_lens)]
-        items = plan_diff_tiles(case.q_lens, pos0, case.H // case.G, ops.attention_diff_mma_rows())
-        ops.attention_diff_mma(case.q_dev, out, i32(items), len(items) // 2, i32(q_start), i32(case.q_lens), i32(pos0),
-                               i32(np.arange(len(case.lengths))), i32(case.table), case.kpool, case.vpool, *args)
+        tc5 = kernel == "tc5"
+        plan = plan_diff_attention(case.q_lens, pos0, case.H // case.G, case.G, chunk,
+                                   ops.attention_tc5_diff_rows() if tc5 else ops.attention_diff_mma_rows(),
+                                   splits=int(kernel[4:]) if "-" in kernel else None, quads=tc5)
+        seqs = (i32(q_start), i32(case.q_lens), i32(pos0), i32(np.arange(len(case.lengths))))
+        tail = (i32(case.table), case.kpool, case.vpool) + args
+        if plan["pre"] and tc5:
+            ops.attention_tc5_diff(case.q_dev, out, i32(plan["pre"]), len(plan["pre"]) // 4, *seqs, *tail)
+        elif plan["pre"]:
+            ops.attention_diff_mma(case.q_dev, out, i32(plan["pre"]), len(plan["pre"]) // 2, *seqs, *tail)
+        if plan["dec"]:
+            n = len(plan["slots"]) // 2 * case.G * ops.DIFF_MAX_SPLITS * 2 * ops.DIFF_DECODE_ROWS
+            part_o = torch.full((max(n, 1), case.vdim), float("nan"), device=DEV)
+            part_ml = torch.full((max(n, 1), 2), float("nan"), device=DEV)
+            ops.attention_diff_mma_decode(case.q_dev, out, i32(plan["dec"]), len(plan["dec"]) // 4, i32(plan["slots"] or [0]),
+                                          len(plan["slots"]) // 2, part_o, part_ml, *seqs, *tail)
     ops.check_error_word(err)
     return out
 
@@ -170,12 +186,17 @@ DIFF_SHAPES = [  # lengths, query counts, H, G, dim, vdim, page, block of positi
     ((90, 40), (90, 1), 4, 1, 32, 32, 16, None),
     ((200, 131, 64, 65), (200, 1, 2, 65), 4, 2, 32, 64, 16, 64),
     ((300, 130), (172, 1), 2, 1, 64, 128, 16, 128),
+    ((700, 300, 9), (700, 260, 9), 4, 2, 32, 64, 16, 256),
+    ((1000, 40), (1000, 33), 8, 2, 64, 128, 32, None),
 ]
 
 
-def kernels_for(dtype, dim, vdim):
+def kernels_for(dtype, dim, vdim, page=16):
     from mashbox_b200 import ops
-    return ["simple"] + (["mma"] if dtype == "bfloat16" and ops.attention_diff_mma_supports(dim, vdim) else [])
+    if dtype == "bfloat16" and ops.attention_tc5_diff_supports(dim, vdim, page):
+        return ["simple", "mma", "mma-2", "mma-4", "mma-16", "tc5"]
+    # the tensor-core kernels with the mixer's own plan, and with the short sequences cut into 2, 4 and 16 splits
+    return ["simple"] + (["mma", "mma-2", "mma-4", "mma-16"] if dtype == "bfloat16" and ops.attention_diff_mma_supports(dim, vdim) else [])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -185,7 +206,7 @@ def test_differential_attention_kernels(dtype, shape):
     case = DiffCase(lengths, q_lens, H, G, dim, vdim, page, dtype, seed=len(lengths)).build()
     scale, lam, delta, eps = dim ** -0.5, 0.37, 0.3, 1e-5
     want = case.reference(scale, chunk, lam, delta, eps)
-    for kernel in kernels_for(dtype, dim, vdim):
+    for kernel in kernels_for(dtype, dim, vdim, page):
         kernel_close(run_diff(case, chunk, scale, lam, delta, eps, kernel), want, dtype, f"{kernel} kernel, {shape}")
 
 
@@ -217,7 +238,7 @@ def test_one_loud_key_inside_and_outside_a_block(dtype, dim, vdim, page, chunk):
             qv = loud.q[0][pos, 0, 0]
             loud.k[0][place, 0, 0] = (40.0 * qv / qv.norm() ** 2 / dim ** -0.5).to(TD[dtype]).double()
             quiet.build(), loud.build()
-            for kernel in kernels_for(dtype, dim, vdim):
+            for kernel in kernels_for(dtype, dim, vdim, page):
                 a = run_diff(quiet, chunk, dim ** -0.5, 0.4, 0.2, 1e-6, kernel)[-1].float().cpu().reshape(H, vdim)
                 b = run_diff(loud, chunk, dim ** -0.5, 0.4, 0.2, 1e-6, kernel)[-1].float().cpu().reshape(H, vdim)
                 want = loud.reference(dim ** -0.5, chunk, 0.4, 0.2, 1e-6)[-1].reshape(H, vdim)
