@@ -688,6 +688,10 @@ def run_design(a):
     clocks = Clocks()
     clocks.start()
     out = {}
+    if a.kernels:                               # the single kernels only (also the workload of their ncu captures)
+        print(json.dumps({"impl": "ours", "design": "luzosun", "size": a.size, "prefill_tokens": P, "batch": B, "context": ctx,
+                          "peaks": pk, "kernels": design_kernels(a, z, P, B, ctx, pk), "clocks": clocks.stop()}))
+        return 0
     for name, cfg in cfgs.items():
         rand_ids = lambda n: torch.randint(0, cfg.vocab, (n,), generator=gen).tolist()
         per_request = -(-(ctx + 64) // 64) * 64
@@ -788,7 +792,9 @@ def design_kernels(a, z, P, B, ctx, pk):
         q_start = [i * (N // S) for i in range(S)]
         seqs = (i32(q_start), i32(q_len), i32(pos0))
         rows = i32(list(range(S)))
-        plan = {k: i32(v or [0]) for k, v in plan_diff_attention(q_len, pos0, G, KV, z["block"], ops.attention_diff_mma_rows()).items()}
+        target = int((json.loads(a.options) if a.options else {}).get("attention_target_blocks", 296))
+        plan = {k: i32(v or [0]) for k, v in plan_diff_attention(q_len, pos0, G, KV, z["block"], ops.attention_diff_mma_rows(),
+                                                                 target=target).items()}
         tail = (*seqs, rows, table, kz, vz, H, KV, dim, vd, page, pages, z["block"], dim ** -0.5, 0.4, 0.7, 1e-6, err)
         if form == "prompt":
             us = timed(lambda: ops.attention_diff_mma(q, o, plan["pre"], plan["pre"].numel() // 2, *tail))

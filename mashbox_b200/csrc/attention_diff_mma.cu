@@ -29,6 +29,7 @@ struct DiffParams {
     const int* q_start; const int* q_len; const int* pos0; const int* seq_row;
     const int* table; int max_blocks;
     int H, G, group, page, num_pages, chunk;
+    int page_shift;                         // log2(page) when the page size is a power of two, else -1
     float scale_log2, lam, gain, eps;
     int* err;
 };
@@ -42,30 +43,48 @@ static_assert(DIFF_DIM % 16 == 0 && DIFF_VD % 16 == 0 && DIFF_DIM >= 16 && DIFF_
 static_assert(DIFF_DIM <= 128 && DIFF_VD <= 128, "head sizes up to 128");
 static_assert((size_t)BM * (DIFF_VD + 4) * sizeof(float) <= (size_t)STAGES * STAGE_ELEMS * sizeof(bf16), "the meeting place fits");
 
+// One K/V tile of 64 keys into a stage.  Warp w fetches the eight key rows 8 w .. 8 w + 7; with pages of a power of two
+// of at least 8 positions they lie in one page (tiles start at multiples of 64), so the table is read once per warp and
+// tile; other page sizes look every row up.  Lane l copies 16-byte chunks l and l + 32 of a row's [map 0 | map 1 | values].
 __device__ __forceinline__ void load_kv_tile(bf16* stage, const DiffParams& P, const int* tb, int g, int kb, int lo,
                                              int hi, int tid) {
-    constexpr int CK = DIFF_DIM / 8, CV = DIFF_VD / 8, CT = 2 * CK + CV;
-    for (int cid = tid; cid < BN * CT; cid += THREADS) {
-        const int row = cid / CT, c = cid % CT;
-        const int kp = kb + row;
-        const bf16* src = P.kpool;
+    constexpr int CK = DIFF_DIM / 8, CV = DIFF_VD / 8, CT = 2 * CK + CV, RW = BN / (THREADS / 32);
+    const int warp = tid >> 5, lane = tid & 31;
+    const bool one_page = P.page_shift >= 3;
+    int pg = 0;
+    if (one_page) {
+        const int kp = kb + warp * RW;
+        pg = (kp + RW > lo && kp < hi) ? tb[kp >> P.page_shift] : 0;   // rows outside [lo, hi) are not copied below
+    }
+#pragma unroll
+    for (int i = 0; i < RW; i++) {
+        const int row = warp * RW + i, kp = kb + row;
+        const bf16 *ksrc = P.kpool, *vsrc = P.vpool;
         int bytes = 0;
         if (kp >= lo && kp < hi) {                          // below lo the pages may have been given back
-            const int block = kp / P.page, slot = kp - block * P.page;
-            const int pg = tb[block];
+            int slot;
+            if (one_page) {
+                slot = kp & (P.page - 1);
+            } else {
+                const int block = kp / P.page;
+                slot = kp - block * P.page;
+                pg = tb[block];
+            }
             if (pg >= 0 && pg < P.num_pages) {
                 const size_t r = ((size_t)pg * P.G + g) * P.page + slot;
-                src = c < 2 * CK ? P.kpool + r * (2 * DIFF_DIM) + c * 8 : P.vpool + r * DIFF_VD + (c - 2 * CK) * 8;
+                ksrc += r * (2 * DIFF_DIM);
+                vsrc += r * DIFF_VD;
                 bytes = 16;
             } else {
                 mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
             }
         }
-        bf16* dst;
-        if (c < CK) dst = stage + swz<DIFF_DIM>(row, c);
-        else if (c < 2 * CK) dst = stage + BN * KROW + swz<DIFF_DIM>(row, c - CK);
-        else dst = stage + 2 * BN * KROW + swz<DIFF_VD>(row, c - 2 * CK);
-        cp_async16(dst, src, bytes);
+#pragma unroll
+        for (int c = lane; c < CT; c += 32) {
+            if (c < CK) cp_async16(stage + swz<DIFF_DIM>(row, c), ksrc + c * 8, bytes);
+            else if (c < 2 * CK) cp_async16(stage + BN * KROW + swz<DIFF_DIM>(row, c - CK), ksrc + c * 8, bytes);
+            else cp_async16(stage + 2 * BN * KROW + swz<DIFF_VD>(row, c - 2 * CK), vsrc + (c - 2 * CK) * 8, bytes);
+        }
     }
 }
 
@@ -184,8 +203,10 @@ __global__ void __launch_bounds__(THREADS) attn_diff_mma_kernel(const DiffParams
                 s[j][e] = p;
             }
         }
+        if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {       // no row of the warp moved its maximum: skip
 #pragma unroll
-        for (int d = 0; d < DT; d++) { o[d][0] *= corr[0]; o[d][1] *= corr[0]; o[d][2] *= corr[1]; o[d][3] *= corr[1]; }
+            for (int d = 0; d < DT; d++) { o[d][0] *= corr[0]; o[d][1] *= corr[0]; o[d][2] *= corr[1]; o[d][3] *= corr[1]; }
+        }
 #pragma unroll
         for (int kk = 0; kk < NT / 2; kk++) {
             uint32_t a[4];
@@ -407,8 +428,10 @@ __global__ void __launch_bounds__(THREADS, 2) attn_diff_mma_decode_kernel(const 
                 s[j][e] = p;
             }
         }
+        if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {       // no row of the warp moved its maximum: skip
 #pragma unroll
-        for (int d = 0; d < DT; d++) { o[d][0] *= corr[0]; o[d][1] *= corr[0]; o[d][2] *= corr[1]; o[d][3] *= corr[1]; }
+            for (int d = 0; d < DT; d++) { o[d][0] *= corr[0]; o[d][1] *= corr[0]; o[d][2] *= corr[1]; o[d][3] *= corr[1]; }
+        }
         uint32_t a[4];
         a[0] = pack_bf16(s[0][0], s[0][1]);
         a[1] = pack_bf16(s[0][2], s[0][3]);
@@ -540,6 +563,8 @@ static void fill_params(DiffParams& P, const void* q, void* out, const void* kpo
     P.items = nullptr; P.q_start = q_start; P.q_len = q_len; P.pos0 = pos0; P.seq_row = seq_row;
     P.table = table; P.max_blocks = max_blocks;
     P.H = H; P.G = G; P.group = H / G; P.page = page; P.num_pages = num_pages; P.chunk = chunk;
+    P.page_shift = -1;
+    for (int sft = 0; sft < 31; sft++) if ((1 << sft) == page) P.page_shift = sft;
     P.scale_log2 = scale * 1.4426950408889634f; P.lam = lam; P.gain = gain; P.eps = eps; P.err = err;
 }
 
@@ -591,11 +616,9 @@ MB_API int mb_attn_diff_mma(const void* q, void* out, const void* kpool, const v
         ready = true;
     }
     DiffParams P;
-    P.q = (const bf16*)q; P.out = (bf16*)out; P.kpool = (const bf16*)kpool; P.vpool = (const bf16*)vpool;
-    P.items = (const int2*)items; P.q_start = q_start; P.q_len = q_len; P.pos0 = pos0; P.seq_row = seq_row;
-    P.table = table; P.max_blocks = max_blocks;
-    P.H = H; P.G = G; P.group = H / G; P.page = page; P.num_pages = num_pages; P.chunk = chunk;
-    P.scale_log2 = scale * 1.4426950408889634f; P.lam = lam; P.gain = gain; P.eps = eps; P.err = err;
+    fill_params(P, q, out, kpool, vpool, q_start, q_len, pos0, seq_row, table, max_blocks, H, G, page, num_pages, chunk, scale,
+                lam, gain, eps, err);
+    P.items = (const int2*)items;
     attn_diff_mma_kernel<<<dim3(n_items, G), THREADS, SMEM_BYTES, st>>>(P);
     MB_LAUNCH_CHECK();
     return 0;

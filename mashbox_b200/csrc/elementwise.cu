@@ -253,8 +253,15 @@ __global__ void __launch_bounds__(256) add_rmsnorm_pair_kernel(float* __restrict
 // ------------------------------------------------------------------------------------------------ xIELU
 // out = ap * z^2 + z / 2 for z > 0, an * (exp(z) - 1 - z) + z / 2 otherwise; ap and an are the layer's two numbers as
 // the host made them (softplus of the stored ones, the second plus one half).  Float arithmetic.
+template <typename T> __device__ __forceinline__ float xielu_tail(float z);      // exp(z) - 1 - z for z <= 0
+template <> __device__ __forceinline__ float xielu_tail<float>(float z) { return expm1f(z) - z; }
+// bf16 results: the fast exponential; where z is so small that the difference cancels, the term it feeds is far below a
+// rounding step of z / 2
+template <> __device__ __forceinline__ float xielu_tail<__nv_bfloat16>(float z) { return __expf(z) - 1.0f - z; }
+template <typename T>
 __device__ __forceinline__ float xielu(float z, float ap, float an) {
-    return z > 0.0f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+    const float pos = fmaf(ap * z, z, 0.5f * z), neg = fmaf(an, xielu_tail<T>(fminf(z, 0.0f)), 0.5f * z);
+    return z > 0.0f ? pos : neg;
 }
 template <typename T, bool VEC>
 __global__ void xielu_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total, float ap, float an) {
@@ -264,10 +271,10 @@ __global__ void xielu_kernel(const T* __restrict__ in, T* __restrict__ out, size
         float v[8];
         load8(in + i * 8, v);
 #pragma unroll
-        for (int e = 0; e < 8; e++) v[e] = xielu(v[e], ap, an);
+        for (int e = 0; e < 8; e++) v[e] = xielu<T>(v[e], ap, an);
         store8(out + i * 8, v);
     } else if (i < total) {
-        mb_store(out + i, xielu(mb_load(in + i), ap, an));
+        mb_store(out + i, xielu<T>(mb_load(in + i), ap, an));
     }
 }
 

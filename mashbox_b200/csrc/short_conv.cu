@@ -266,10 +266,11 @@ __global__ void __launch_bounds__(128) short_conv_vec_kernel(const T* __restrict
     store8(out + (size_t)n * C + c, y);
 }
 
-// rotates (when pair) and stores eight channels from c on (and their partners) of token n
+// rotates (when pair; cs: the token's cosines and sines, one per rotated pair) and stores eight channels from c on (and
+// their partners) of token n
 template <typename T>
 __device__ __forceinline__ void qkv_emit8(const ConvQkv& p, T* q_out, T* kpool, T* vpool, int n, int c, float (&y0)[8],
-                                          float (&y1)[8], bool pair, int* err) {
+                                          float (&y1)[8], bool pair, const float2* cs, int* err) {
     const int qk = (p.QU + p.KU) * p.dim;
     const int pos = p.positions[n];
     size_t slot = 0;
@@ -290,9 +291,8 @@ __device__ __forceinline__ void qkv_emit8(const ConvQkv& p, T* q_out, T* kpool, 
         const int d = c % p.dim;
 #pragma unroll
         for (int e = 0; e < 8; e++) {
-            float sn, cs;
-            sincosf((float)pos * p.freqs[d + e], &sn, &cs);
-            const float r0 = y0[e] * cs - y1[e] * sn, r1 = y1[e] * cs + y0[e] * sn;
+            const float2 t = cs[d + e];                             // (cos, sin) of the token's angle for this pair
+            const float r0 = y0[e] * t.x - y1[e] * t.y, r1 = y1[e] * t.x + y0[e] * t.y;
             y0[e] = r0; y1[e] = r1;
         }
     }
@@ -314,8 +314,20 @@ __global__ void __launch_bounds__(128) conv_rope_kv_write_vec_kernel(const T* __
                                                                     size_t slot_stride, ConvSeq sq, ConvQkv p,
                                                                     T* __restrict__ q_out, T* __restrict__ kpool,
                                                                     T* __restrict__ vpool, int taps, int* err) {
+    extern __shared__ float2 rope_cs[];                             // (cos, sin) of the token's RD / 2 pairs
     const int C = (p.QU + p.KU) * p.dim + p.VH * p.vdim;
     const int n = blockIdx.x;
+    const int s = sq.tok_seq[n], a = sq.q_start[s], t = n - a;
+    if (t < taps - 1) return;                                       // a head of a stretch: the other kernel's (whole block)
+    if (p.freqs) {
+        const float pos = (float)p.positions[n];
+        for (int i = threadIdx.x; i < p.RD / 2; i += blockDim.x) {
+            float sn, cs;
+            sincosf(pos * p.freqs[i], &sn, &cs);
+            rope_cs[i] = make_float2(cs, sn);
+        }
+        __syncthreads();
+    }
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
     if (c >= C) return;
     bool pair = false;
@@ -325,12 +337,10 @@ __global__ void __launch_bounds__(128) conv_rope_kv_write_vec_kernel(const T* __
         else if (d < p.RD) return;
     }
     const int c1 = c + p.RD / 2;
-    const int s = sq.tok_seq[n], a = sq.q_start[s], t = n - a;
-    if (t < taps - 1) return;                                       // a head of a stretch: the other kernel's
     float y0[8], y1[8];
     conv_inner8(in, C, bias, w, taps, n, c, y0);
     if (pair) conv_inner8(in, C, bias, w, taps, n, c1, y1);
-    qkv_emit8(p, q_out, kpool, vpool, n, c, y0, y1, pair, err);
+    qkv_emit8(p, q_out, kpool, vpool, n, c, y0, y1, pair, rope_cs, err);
 }
 
 // ------------------------------------------------------------------------------------------------ launches
@@ -392,7 +402,8 @@ static int conv_qkv_launch(const void* in, const float* bias, const float* w, fl
         (((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)kpool | (uintptr_t)vpool | (uintptr_t)state | (uintptr_t)bias) & 15) == 0) {
         const int groups = C / 8, threads = groups >= 128 ? 128 : ((groups + 31) / 32) * 32;
         if (N > S || taps == 1)                 // N == S: every stretch is one token, a head
-            conv_rope_kv_write_vec_kernel<T><<<dim3(N, (groups + threads - 1) / threads), threads, 0, st>>>(
+            conv_rope_kv_write_vec_kernel<T><<<dim3(N, (groups + threads - 1) / threads), threads,
+                                               (freqs ? RD / 2 : 0) * sizeof(float2), st>>>(
                 (const T*)in, bias, w, state, (size_t)slot_stride, sq, p, (T*)q_out, (T*)kpool, (T*)vpool, taps, err);
         if (taps > 1) {
             const int th = C >= 256 ? 256 : ((C + 31) / 32) * 32;

@@ -133,3 +133,37 @@ def test_rotary_part_divides_by_the_factor():
         part = RotaryEncoding(head_dim=dims + 8, rotary_dim=dims, theta=base, pairing="halves",
                               scaling=("divide", factor) if factor else None)
         assert np.allclose(part.frequencies(), plain.rotary_frequencies(base, dims, factor), rtol=3e-7, atol=0)
+
+
+def test_random_folder_loads_and_one_error_lists_everything_wrong(tmp_path):
+    """the command line's random-weights mode writes a folder the loader reads back; a tensor too many, one too few
+    and one of the wrong shape come out in ONE error"""
+    import json
+    import math
+    import os
+
+    from mashbox_b200.cli import main as cli
+    from mashbox_b200.engine.loading import build_model, read_config_file
+    from mashbox_b200.errors import WeightError
+    from mashbox_b200.weights.safetensors_io import DictSource, SafetensorsSource
+    cfg_path = tmp_path / "c.json"
+    cfg_path.write_text(json.dumps(L.LUZ_P.to_hf()))
+    folder = str(tmp_path / "model")
+    assert cli(["random", folder, "--config", str(cfg_path), "--seed", "3", "--store", "float32"]) == 0
+    source = SafetensorsSource(folder)
+    model = build_model(read_config_file(folder), source, "float32", "cpu")
+    mixer = model.layers[1].mixer
+    assert mixer.shares_kv and mixer.w.shape == (6 * 32, 64) and mixer.wconv.shape == (2, 6 * 32)
+    t = {n: source.get(n).double() for n in ("l1.mix.lq1", "l1.mix.lk1", "l1.mix.lq2", "l1.mix.lk2")}
+    lam = math.exp(float((t["l1.mix.lq1"] * t["l1.mix.lk1"]).sum())) - math.exp(float((t["l1.mix.lq2"] * t["l1.mix.lk2"]).sum())) + 0.1
+    assert abs(mixer.lam - lam) < 1e-12
+    assert model.layers[1].ffn is None and model.layers[1].norm2 is None
+    tensors = {n: source.get(n) for n in source.names()}
+    source.close()
+    tensors["l1.mix.k"] = torch.zeros(64, 64)                  # a borrowing layer has no key projection
+    del tensors["l2.canon1"]
+    tensors["l0.mlp.act"] = torch.zeros(3)
+    with pytest.raises(WeightError) as e:
+        build_model(L.LUZ_P.to_hf(), DictSource(tensors), "float32", "cpu")
+    msg = str(e.value)
+    assert "l2.canon1" in msg and "l1.mix.k" in msg and "l0.mlp.act" in msg
