@@ -43,47 +43,77 @@ static_assert(DIFF_DIM % 16 == 0 && DIFF_VD % 16 == 0 && DIFF_DIM >= 16 && DIFF_
 static_assert(DIFF_DIM <= 128 && DIFF_VD <= 128, "head sizes up to 128");
 static_assert((size_t)BM * (DIFF_VD + 4) * sizeof(float) <= (size_t)STAGES * STAGE_ELEMS * sizeof(bf16), "the meeting place fits");
 
-// One K/V tile of 64 keys into a stage.  Warp w fetches the eight key rows 8 w .. 8 w + 7; with pages of a power of two
-// of at least 8 positions they lie in one page (tiles start at multiples of 64), so the table is read once per warp and
-// tile; other page sizes look every row up.  Lane l copies 16-byte chunks l and l + 32 of a row's [map 0 | map 1 | values].
+// One K/V tile of 64 keys into a stage.  Warp w fetches the eight key rows 8 w .. 8 w + 7; lane l copies 16-byte chunks l
+// and l + 32 of a row's [map 0 | map 1 | values], so what a lane copies (which of the three sub-tiles, which chunk of
+// its row) is the same for every row and tile.  With pages of a power of two of at least 8 positions the eight rows lie
+// in one page, side by side (tiles start at multiples of 64): the table is read once per warp and tile and a row's
+// address is the first row's plus a constant.  Other page sizes look every row up.
+struct GatherLane {                         // what a lane copies, chunk l (j = 0) and chunk l + 32 (j = 1)
+    bool on[2], is_v[2];
+    int cc[2];                              // chunk within its sub-tile's row
+    int sub[2];                             // element offset of the sub-tile in a stage
+    int src[2];                             // element offset of the chunk in its source row
+};
+__device__ __forceinline__ GatherLane gather_lane(int lane) {
+    constexpr int CK = DIFF_DIM / 8, CV = DIFF_VD / 8, CT = 2 * CK + CV;
+    GatherLane L;
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const int c = lane + 32 * j;
+        L.on[j] = c < CT;
+        L.is_v[j] = c >= 2 * CK;
+        L.cc[j] = c < CK ? c : (c < 2 * CK ? c - CK : c - 2 * CK);
+        L.sub[j] = c < CK ? 0 : (c < 2 * CK ? BN * KROW : 2 * BN * KROW);
+        L.src[j] = (c < 2 * CK ? c : c - 2 * CK) * 8;
+    }
+    return L;
+}
+
 __device__ __forceinline__ void load_kv_tile(bf16* stage, const DiffParams& P, const int* tb, int g, int kb, int lo,
                                              int hi, int tid) {
-    constexpr int CK = DIFF_DIM / 8, CV = DIFF_VD / 8, CT = 2 * CK + CV, RW = BN / (THREADS / 32);
+    constexpr int CT = 2 * (DIFF_DIM / 8) + DIFF_VD / 8, RW = BN / (THREADS / 32);
     const int warp = tid >> 5, lane = tid & 31;
+    const GatherLane L = gather_lane(lane);
     const bool one_page = P.page_shift >= 3;
-    int pg = 0;
+    const bf16 *k0 = P.kpool, *v0 = P.vpool;                // the warp's first row (one_page)
+    bool have = false;
     if (one_page) {
         const int kp = kb + warp * RW;
-        pg = (kp + RW > lo && kp < hi) ? tb[kp >> P.page_shift] : 0;   // rows outside [lo, hi) are not copied below
+        if (kp + RW > lo && kp < hi) {                      // rows outside [lo, hi) are not copied below
+            const int pg = tb[kp >> P.page_shift];
+            if (pg >= 0 && pg < P.num_pages) {
+                const size_t r = ((size_t)pg * P.G + g) * P.page + (kp & (P.page - 1));
+                k0 += r * (2 * DIFF_DIM);
+                v0 += r * DIFF_VD;
+                have = true;
+            } else {
+                mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+            }
+        }
     }
 #pragma unroll
     for (int i = 0; i < RW; i++) {
         const int row = warp * RW + i, kp = kb + row;
-        const bf16 *ksrc = P.kpool, *vsrc = P.vpool;
-        int bytes = 0;
-        if (kp >= lo && kp < hi) {                          // below lo the pages may have been given back
-            int slot;
-            if (one_page) {
-                slot = kp & (P.page - 1);
-            } else {
-                const int block = kp / P.page;
-                slot = kp - block * P.page;
-                pg = tb[block];
-            }
+        const bf16 *ksrc = k0 + i * (2 * DIFF_DIM), *vsrc = v0 + i * DIFF_VD;
+        int bytes = (have && kp >= lo && kp < hi) ? 16 : 0; // below lo the pages may have been given back
+        if (!one_page && kp >= lo && kp < hi) {
+            const int block = kp / P.page, slot = kp - block * P.page;
+            const int pg = tb[block];
             if (pg >= 0 && pg < P.num_pages) {
                 const size_t r = ((size_t)pg * P.G + g) * P.page + slot;
-                ksrc += r * (2 * DIFF_DIM);
-                vsrc += r * DIFF_VD;
+                ksrc = P.kpool + r * (2 * DIFF_DIM);
+                vsrc = P.vpool + r * DIFF_VD;
                 bytes = 16;
             } else {
                 mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
             }
         }
+        if (bytes == 0) { ksrc = P.kpool; vsrc = P.vpool; } // nothing is read, but the address must be a valid one
 #pragma unroll
-        for (int c = lane; c < CT; c += 32) {
-            if (c < CK) cp_async16(stage + swz<DIFF_DIM>(row, c), ksrc + c * 8, bytes);
-            else if (c < 2 * CK) cp_async16(stage + BN * KROW + swz<DIFF_DIM>(row, c - CK), ksrc + c * 8, bytes);
-            else cp_async16(stage + 2 * BN * KROW + swz<DIFF_VD>(row, c - 2 * CK), vsrc + (c - 2 * CK) * 8, bytes);
+        for (int j = 0; j < (CT > 32 ? 2 : 1); j++) {
+            if (!L.on[j]) continue;
+            const int off = L.is_v[j] ? swz<DIFF_VD>(row, L.cc[j]) : swz<DIFF_DIM>(row, L.cc[j]);
+            cp_async16(stage + L.sub[j] + off, (L.is_v[j] ? vsrc : ksrc) + L.src[j], bytes);
         }
     }
 }

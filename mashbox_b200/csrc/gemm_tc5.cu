@@ -28,11 +28,13 @@
 #define G_B_BYTES (G_BN * G_BK * 2)
 #define G_STAGE_BYTES (G_A_BYTES + G_B_BYTES)
 
-// MODE 0: bf16 out (N, M); 1: SwiGLU, W has 2 * M rows, bf16 out (N, M); 2: float out (N, M)
+// MODE 0: bf16 out (N, M); 1: SwiGLU, W has 2 * M rows, bf16 out (N, M); 2: float out (N, M); 3: bf16 out (N, M) =
+// xIELU of the product (ap z^2 + z / 2 for z > 0, an (e^z - 1 - z) + z / 2 otherwise)
 template <int MODE>
 __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant__ CUtensorMap amap,
                                                            const __grid_constant__ CUtensorMap wmap,
-                                                           void* __restrict__ out, int N, int M, int K, int* err) {
+                                                           void* __restrict__ out, int N, int M, int K, float ap,
+                                                           float an, int* err) {
     constexpr int FEATS = MODE == 1 ? 128 : 256;          // output features of one tile
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -131,6 +133,15 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
                     }
                 } else {
                     tmem_ld_wait();
+                    if (MODE == 3) {
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            // the product passes through bf16 as it does when the activation is a kernel of its own
+                            const float z = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
+                            const float neg = fmaf(an, __expf(fminf(z, 0.0f)) - 1.0f - fminf(z, 0.0f), 0.5f * z);
+                            r[i] = __float_as_uint(z > 0.0f ? fmaf(ap * z, z, 0.5f * z) : neg);
+                        }
+                    }
                 }
                 if (tok < N) {
                     if (MODE == 2) {
@@ -170,7 +181,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
 }
 
 template <int MODE>
-static int tc5_launch(const void* act, const void* W, void* out, int N, int M, int K, int* err, cudaStream_t st) {
+static int tc5_launch(const void* act, const void* W, void* out, int N, int M, int K, int* err, cudaStream_t st,
+                      float ap = 0.0f, float an = 0.0f) {
     if (N == 0 || M == 0) return 0;
     if (K % 8 || M % 8 || K < 8 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(act) & 15) ||
         (reinterpret_cast<uintptr_t>(out) & 15))
@@ -194,7 +206,7 @@ static int tc5_launch(const void* act, const void* W, void* out, int N, int M, i
     }
     const int feats = MODE == 1 ? 128 : 256;
     const int tiles = ((N + G_BM - 1) / G_BM) * ((M + feats - 1) / feats);
-    gemm_tc5_kernel<MODE><<<tiles < sms ? tiles : sms, 192, smem, st>>>(amap, wmap, out, N, M, K, err);
+    gemm_tc5_kernel<MODE><<<tiles < sms ? tiles : sms, 192, smem, st>>>(amap, wmap, out, N, M, K, ap, an, err);
     MB_LAUNCH_CHECK();
     return 0;
 }
@@ -208,6 +220,12 @@ MB_API int mb_gemm_tc5_bf16(const void* act, const void* W, void* out, int N, in
 MB_API int mb_gemm_tc5_swiglu_bf16(const void* act, const void* W, void* out, int N, int M, int K, int* err,
                                    cudaStream_t st) {
     return tc5_launch<1>(act, W, out, N, M, K, err, st);
+}
+// out (N, M) = xIELU(act W^T) with the layer's two numbers as the host made them (softplus of the stored ones, the second
+// plus one half)
+MB_API int mb_gemm_tc5_xielu_bf16(const void* act, const void* W, void* out, int N, int M, int K, float ap, float an,
+                                  int* err, cudaStream_t st) {
+    return tc5_launch<3>(act, W, out, N, M, K, err, st, ap, an);
 }
 MB_API int mb_gemm_tc5_f32out(const void* act, const void* W, void* out, int N, int M, int K, int* err, cudaStream_t st) {
     return tc5_launch<2>(act, W, out, N, M, K, err, st);

@@ -523,6 +523,25 @@ def fused_swiglu_supports(N, F, K):
     return gemv_supports(N, K, "swiglu") or stream_supports(N, K) or tc5_supports(N, F, K, "swiglu")
 
 
+def fused_xielu_supports(N, F, K):
+    """the up product of a prompt portion with the xIELU activation in its epilogue (the tcgen05 product)"""
+    return tc5_supports(N, F, K, "swiglu")
+
+
+def linear_xielu(a, w, out, ap, an):
+    """a (N, K) bf16, w (F, K) bf16 -> out (N, F) bf16 = xielu(a W^T), one kernel; shapes fused_xielu_supports() takes"""
+    _cuda(a, w, out)
+    N, K = a.shape
+    if not (fused_xielu_supports(N, out.shape[1], K) and a.dtype == torch.bfloat16 and a.is_contiguous()
+            and w.is_contiguous() and out.is_contiguous()):
+        raise KernelError("linear_xielu: no fused kernel takes these sizes")
+    f = _fn("gemm_tc5", "mb_gemm_tc5_xielu_bf16", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
+                                                   c_void_p, c_void_p])
+    _check(f(_p(a), _p(w), _p(out), N, out.shape[1], K, float(ap), float(an), _p(error_word(a.device)), _stream()),
+           "gemm_tc5_xielu")
+    return out
+
+
 def linear_swiglu(a, wgu, out):
     """a (N, K) bf16, wgu (2F, K) = [gate rows | up rows] -> out (N, F) = silu(a Wg^T) * (a Wu^T), one kernel: the
     tcgen05 product for prompt portions, the matrix-vector or the weight-streaming kernel for decode batches (where enabled).

@@ -80,11 +80,15 @@ class DenseXielu:
     def forward(self, ctx, h, out="delta"):
         """out: the workspace buffer the result is left in (a block that runs this part beside its mixer names another
         one than the mixer's)"""
+        import torch
         N = ctx.N
-        z = ctx.ws.get("ffn_up", N, (self.F,), ctx.dtype)
-        ctx.ops.linear(h, self.wu, out=z)
         a = ctx.ws.get("ffn_act", N, (self.F,), ctx.dtype)
-        ctx.ops.xielu(z, a, self.ap, self.an)
+        if ctx.dtype == torch.bfloat16 and ctx.ops.fused_xielu_supports(N, self.F, self.D):
+            ctx.ops.linear_xielu(h, self.wu, a, self.ap, self.an)       # the product with the activation in its epilogue
+        else:
+            z = ctx.ws.get("ffn_up", N, (self.F,), ctx.dtype)
+            ctx.ops.linear(h, self.wu, out=z)
+            ctx.ops.xielu(z, a, self.ap, self.an)
         y = ctx.ws.get(out, N, (self.D,), ctx.dtype)
         ctx.ops.linear(a, self.wd, out=y)
         return y, None

@@ -98,6 +98,21 @@ def test_xielu_and_pair_of_norms(dtype):
         assert torch.equal(xs2.cpu(), x)                                  # picked rows leave the stream alone
 
 
+def test_up_product_with_the_activation_in_its_epilogue():
+    from mashbox_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    sp = lambda t: float(np.log1p(np.exp(t)))
+    for N, K, F in ((200, 64, 96), (129, 72, 264)):
+        if not ops.fused_xielu_supports(N, F, K):
+            pytest.skip("the fused product does not take these sizes")
+        x = torch.randn(N, K, generator=g).to(torch.bfloat16)
+        w = (torch.randn(F, K, generator=g) * K ** -0.5 * 2).to(torch.bfloat16)
+        out = torch.empty(N, F, device=DEV, dtype=torch.bfloat16)
+        ops.linear_xielu(x.to(DEV), w.to(DEV), out, sp(0.4), 0.5 + sp(-0.3))
+        kernel_close(out, plain.xielu(x.double() @ w.double().T, 0.4, -0.3), "bfloat16", f"fused up product {N}x{K}x{F}")
+    ops.check_error_word(ops.error_word(DEV))
+
+
 class DiffCase:
     """S sequences with two-map queries and keys in shuffled pages; the step's queries are each sequence's last ones"""
 
