@@ -38,10 +38,11 @@ constexpr int BM = 64, BN = 64, THREADS = 256, STAGES = 2;
 constexpr int KROW = tile_row<DIFF_DIM>(), VROW = tile_row<DIFF_VD>();
 constexpr int STAGE_ELEMS = 2 * BN * KROW + BN * VROW;          // keys of map 0, keys of map 1, values
 constexpr int Q_ELEMS = 2 * BM * KROW;
-constexpr size_t SMEM_BYTES = (size_t)(Q_ELEMS + STAGES * STAGE_ELEMS) * sizeof(bf16);
+constexpr size_t cmax(size_t a, size_t b) { return a > b ? a : b; }
+// the stages are also where the two maps meet at the end ([64 rows][VD + 4] floats): room for the larger of the two
+constexpr size_t SMEM_BYTES = Q_ELEMS * sizeof(bf16) + cmax((size_t)STAGES * STAGE_ELEMS * sizeof(bf16), (size_t)BM * (DIFF_VD + 4) * sizeof(float));
 static_assert(DIFF_DIM % 16 == 0 && DIFF_VD % 16 == 0 && DIFF_DIM >= 16 && DIFF_VD >= 16, "head sizes are multiples of 16");
 static_assert(DIFF_DIM <= 128 && DIFF_VD <= 128, "head sizes up to 128");
-static_assert((size_t)BM * (DIFF_VD + 4) * sizeof(float) <= (size_t)STAGES * STAGE_ELEMS * sizeof(bf16), "the meeting place fits");
 
 // One K/V tile of 64 keys into a stage.  Warp w fetches the eight key rows 8 w .. 8 w + 7; lane l copies 16-byte chunks l
 // and l + 32 of a row's [map 0 | map 1 | values], so what a lane copies (which of the three sub-tiles, which chunk of
@@ -309,9 +310,9 @@ __global__ void __launch_bounds__(THREADS) attn_diff_mma_kernel(const DiffParams
 // below finishes the rows.  A work item is (sequence, split, n_splits, slot of the partial results).
 constexpr int DBM = 16, DSTAGES = 3, MAX_SPLITS = 16;
 constexpr int DQ_ELEMS = 2 * DBM * KROW;
-constexpr size_t DSMEM_BYTES = (size_t)(DQ_ELEMS + DSTAGES * STAGE_ELEMS) * sizeof(bf16);
-static_assert((size_t)(8 * DBM * DIFF_VD + 2 * 8 * DBM) * sizeof(float) <= (size_t)DSTAGES * STAGE_ELEMS * sizeof(bf16),
-              "the quarters' meeting place fits");
+// the stages are also where the quarters meet at the end ([8 warps][16 rows][VD] floats, maxima and weights)
+constexpr size_t DSMEM_BYTES = DQ_ELEMS * sizeof(bf16) + cmax((size_t)DSTAGES * STAGE_ELEMS * sizeof(bf16),
+                                                              (size_t)(8 * DBM * DIFF_VD + 2 * 8 * DBM) * sizeof(float));
 
 struct DiffDecodeParams {
     DiffParams p;

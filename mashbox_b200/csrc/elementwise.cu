@@ -165,6 +165,14 @@ __global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict_
     }
 }
 
+// what the kernel below needs to fold a short causal convolution of its first output in, for steps in which every
+// sequence brings ONE token: the filters tap by tap (taps, D), the state tensor (slots, taps - 1, D) with its slot stride,
+// the state slot of every row; w null: no convolution
+struct PairConv { const float* w; float* state; size_t slot_stride; const int* slots; int taps; };
+template <typename T> __device__ __forceinline__ float mb_round(float v);
+template <> __device__ __forceinline__ float mb_round<float>(float v) { return v; }
+template <> __device__ __forceinline__ float mb_round<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
 // ------------------------------------------------------------------------------------------------ add + two RMSNorms
 // For a block whose mixer and feed-forward read the same stream through norms of their own: v = x[r] (+ d1[r]) (+ d2[r])
 // -- the two outputs of the block before, added into the float stream here -- written back to x unless rows picks
@@ -175,7 +183,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_pair_kernel(float* __restrict
                                                               const T* __restrict__ d2, const int* __restrict__ rows,
                                                               const float* __restrict__ w1, const float* __restrict__ w2,
                                                               float eps, T* __restrict__ out1, T* __restrict__ out2,
-                                                              int D) {
+                                                              int D, PairConv cv) {
     __shared__ float scratch[32];
     const int i = blockIdx.x;
     const size_t r = rows ? (size_t)rows[i] : (size_t)i;
@@ -231,6 +239,25 @@ __global__ void __launch_bounds__(256) add_rmsnorm_pair_kernel(float* __restrict
             load8(w1 + c * 8, g);
 #pragma unroll
             for (int e = 0; e < 8; e++) t[e] = v[e] * inv * g[e];
+            if (cv.w) {
+                // one-token stretches: the causal convolution of the first output with the row's state, and the new state
+                // (the sums of the convolution kernel's head of a stretch, in its order, on the row as it would be stored)
+                float* st = cv.state + (size_t)cv.slots[i] * cv.slot_stride + c * 8;
+                float acc[8], h[8], wt[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) { t[e] = mb_round<T>(t[e]); acc[e] = 0.0f; }
+                for (int j = 0; j < cv.taps - 1; j++) {
+                    load8(st + (size_t)j * D, h);
+                    load8(cv.w + (size_t)j * D + c * 8, wt);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) acc[e] = fmaf(wt[e], h[e], acc[e]);
+                    if (j > 0) store8(st + (size_t)(j - 1) * D, h);
+                }
+                store8(st + (size_t)(cv.taps - 2) * D, t);
+                load8(cv.w + (size_t)(cv.taps - 1) * D + c * 8, wt);
+#pragma unroll
+                for (int e = 0; e < 8; e++) t[e] = fmaf(wt[e], t[e], acc[e]) + t[e];
+            }
             store8(out1 + (size_t)i * D + c * 8, t);
             if (w2) {
                 load8(w2 + c * 8, g);
@@ -518,15 +545,18 @@ MB_API int mb_add_rmsnorm_bf16(float* x, const void* delta, const float* dbias, 
 
 template <typename T>
 static int add_rmsnorm_pair_launch(float* x, const void* d1, const void* d2, const int* rows, const float* w1,
-                                   const float* w2, float eps, void* out1, void* out2, int n_out, int D, cudaStream_t st) {
+                                   const float* w2, float eps, void* out1, void* out2, int n_out, int D, cudaStream_t st,
+                                   PairConv cv = PairConv{nullptr, nullptr, 0, nullptr, 0}) {
     if (n_out == 0) return 0;
     if (w2 && !out2) return -2;
+    if (cv.w && (D % 8 || rows || cv.taps < 2 || cv.slot_stride % 4 || ((uintptr_t)cv.state & 15) || ((uintptr_t)cv.w & 15)))
+        return -2;
     if (D % 8 == 0)
         add_rmsnorm_pair_kernel<T, true><<<n_out, 256, 0, st>>>(x, (const T*)d1, (const T*)d2, rows, w1, w2, eps, (T*)out1,
-                                                                (T*)out2, D);
+                                                                (T*)out2, D, cv);
     else
         add_rmsnorm_pair_kernel<T, false><<<n_out, 256, 0, st>>>(x, (const T*)d1, (const T*)d2, rows, w1, w2, eps,
-                                                                 (T*)out1, (T*)out2, D);
+                                                                 (T*)out1, (T*)out2, D, cv);
     MB_LAUNCH_CHECK();
     return 0;
 }
@@ -537,6 +567,20 @@ MB_API int mb_add_rmsnorm_pair_f32(float* x, const void* d1, const void* d2, con
 MB_API int mb_add_rmsnorm_pair_bf16(float* x, const void* d1, const void* d2, const int* rows, const float* w1,
                                     const float* w2, float eps, void* out1, void* out2, int n_out, int D, cudaStream_t st) {
     return add_rmsnorm_pair_launch<__nv_bfloat16>(x, d1, d2, rows, w1, w2, eps, out1, out2, n_out, D, st);
+}
+// The same for a step in which every sequence brings one token, with out1 <- out1 + causal_conv(out1): cw (taps, D) the
+// filters tap by tap, state (slots, taps - 1, D) floats slot_stride apart, slots[i] the state slot of row i.  D % 8 == 0.
+MB_API int mb_add_rmsnorm_pair_conv_f32(float* x, const void* d1, const void* d2, const float* w1, const float* w2, float eps,
+                                        void* out1, void* out2, int n_out, int D, const float* cw, float* state,
+                                        long long slot_stride, const int* slots, int taps, cudaStream_t st) {
+    return add_rmsnorm_pair_launch<float>(x, d1, d2, nullptr, w1, w2, eps, out1, out2, n_out, D, st,
+                                          PairConv{cw, state, (size_t)slot_stride, slots, taps});
+}
+MB_API int mb_add_rmsnorm_pair_conv_bf16(float* x, const void* d1, const void* d2, const float* w1, const float* w2, float eps,
+                                         void* out1, void* out2, int n_out, int D, const float* cw, float* state,
+                                         long long slot_stride, const int* slots, int taps, cudaStream_t st) {
+    return add_rmsnorm_pair_launch<__nv_bfloat16>(x, d1, d2, nullptr, w1, w2, eps, out1, out2, n_out, D, st,
+                                                  PairConv{cw, state, (size_t)slot_stride, slots, taps});
 }
 
 template <typename T>

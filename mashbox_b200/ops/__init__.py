@@ -176,6 +176,22 @@ def add_rmsnorm_pair(x, delta1, delta2, weight1, weight2, eps, out1, out2=None, 
              out1.shape[0], D, _stream()), "add_rmsnorm_pair")
 
 
+def add_rmsnorm_pair_conv(x, delta1, delta2, weight1, weight2, eps, out1, out2, conv_w, state, slots):
+    """add_rmsnorm_pair for a step in which every sequence brings one token, with the short causal convolution of the
+    first output folded in: out1 <- out1 + conv(out1) over the row's state.  conv_w (taps, D) float32 tap by tap, state
+    (slots, (taps - 1) D) float32 (a view; replaced by the step's), slots int32 (N,) the state slot of every row.  D a
+    multiple of 8, taps at least 2; the same bits as add_rmsnorm_pair followed by short_conv(residual=True)."""
+    _cuda(x, delta1, delta2, weight1, weight2, out1, out2, conv_w, state, slots)
+    D = x.shape[1]
+    if conv_w.shape[1] != D or not conv_w.is_contiguous():
+        raise KernelError("add_rmsnorm_pair_conv: the filters must be a contiguous (taps, width) tensor")
+    f = _fn("elementwise", "mb_add_rmsnorm_pair_conv_" + _suffix(out1.dtype),
+            [c_void_p] * 5 + [c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p,
+                              c_int, c_void_p])
+    _check(f(_p(x), _p(delta1), _p(delta2), _p(weight1), _p(weight2), float(eps), _p(out1), _p(out2), out1.shape[0], D,
+             _p(conv_w), _p(state), state.stride(0), _p(slots), conv_w.shape[0], _stream()), "add_rmsnorm_pair_conv")
+
+
 def xielu(z, out, ap, an):
     """out = ap z^2 + z/2 where z > 0, an (exp(z) - 1 - z) + z/2 elsewhere; z and out (N, F) in the activation dtype"""
     _cuda(z, out)

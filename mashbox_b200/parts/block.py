@@ -98,13 +98,21 @@ class ParallelBlock:
 
     def forward(self, ctx, x, pending, run):
         ctx.after_norm = None
+        conv_done = False
         if self.ffn is not None and hasattr(self.norm1, "forward_pair") and type(self.norm2) is type(self.norm1) \
                 and (self.norm1.width, self.norm1.eps) == (self.norm2.width, self.norm2.eps):
-            a, b = self.norm1.forward_pair(ctx, x, self.norm2, pending)
+            # a step in which every sequence brings one token (N == S follows from the lengths of the step's arrays): the
+            # input convolution is the same kernel's work
+            fold = (self.conv is not None and ctx.N == ctx.S and hasattr(self.conv, "foldable")
+                    and self.conv.foldable(ctx, run.state_id) and not ctx.options.get("no_small_fusion", False))
+            a, b = self.norm1.forward_pair(ctx, x, self.norm2, pending,
+                                           conv=self.conv.folded(ctx, run.state_id) if fold else None)
+            if fold:
+                conv_done = True
         else:
             a = self.norm1.forward(ctx, x, pending)
             b = self.norm2.forward(ctx, x, None) if self.ffn is not None else None
-        if self.conv is not None:
+        if self.conv is not None and not conv_done:
             a = self.conv.forward(ctx, a, run.state_id)
         delta, bias = self.mixer.forward(ctx, a, run)
         if self.ffn is None:

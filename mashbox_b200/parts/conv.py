@@ -53,6 +53,18 @@ class ShortConv:
     def prepare(self, ctx):
         plan_sequences(ctx)
 
+    def foldable(self, ctx, state_id):
+        """the kernel that makes the layer's two norms can take this convolution in for one-token stretches (it reads
+        eight channels at a time, state included)"""
+        if not (self.residual and self.taps > 1 and self.C % 8 == 0):
+            return False
+        view = state_view(ctx, state_id, self.state_offset, self.taps, self.C)
+        return view.stride(0) % 4 == 0 and view.data_ptr() % 16 == 0
+
+    def folded(self, ctx, state_id):
+        """-> (filters, state view) for the norm kernel that folds the convolution in"""
+        return self.weight, state_view(ctx, state_id, self.state_offset, self.taps, self.C)
+
     def forward(self, ctx, h, state_id, out="conv_out"):
         y = ctx.ws.get(out, h.shape[0], (self.C,), ctx.dtype)
         ctx.ops.short_conv(h, self.weight, state_view(ctx, state_id, self.state_offset, self.taps, self.C),

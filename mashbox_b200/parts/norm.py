@@ -40,10 +40,11 @@ class RMSNorm:
             ctx.ops.add_rmsnorm(x, delta, bias, self.weight, self.eps, out, rows)
         return out
 
-    def forward_pair(self, ctx, x, other, pending=None):
+    def forward_pair(self, ctx, x, other, pending=None, conv=None):
         """-> (this norm of x, `other`'s norm of x), x first taking in what is pending ((delta, None) or (delta, None,
         second delta)): for two norms of one width and eps that read the same stream, one kernel and one sum of
-        squares."""
+        squares.  conv = (filters (taps, width), state view): in a step in which every sequence brings one token the
+        kernel also adds the short causal convolution of the first output to it and replaces the state."""
         if other.width != self.width or other.eps != self.eps:
             raise ConfigError("norms with different widths or eps cannot be computed as a pair")
         delta, bias, *more = pending if pending is not None else (None, None)
@@ -53,7 +54,11 @@ class RMSNorm:
             ctx.memo.pop("held", None)
         a = ctx.ws.get("normed", x.shape[0], (self.width,), ctx.dtype)
         b = ctx.ws.get("normed_side", x.shape[0], (self.width,), ctx.dtype)
-        ctx.ops.add_rmsnorm_pair(x, delta, more[0] if more else None, self.weight, other.weight, self.eps, a, b)
+        if conv is not None:
+            ctx.ops.add_rmsnorm_pair_conv(x, delta, more[0] if more else None, self.weight, other.weight, self.eps, a, b,
+                                          conv[0], conv[1], ctx.dev("state_slot"))
+        else:
+            ctx.ops.add_rmsnorm_pair(x, delta, more[0] if more else None, self.weight, other.weight, self.eps, a, b)
         return a, b
 
 

@@ -113,6 +113,30 @@ def test_up_product_with_the_activation_in_its_epilogue():
     ops.check_error_word(ops.error_word(DEV))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_pair_of_norms_with_the_convolution_folded_in_is_the_two_kernels(dtype):
+    """one-token stretches: the norm kernel with the input convolution folded in leaves the same bits, in its outputs
+    and in the state, as the norm kernel followed by the convolution kernel"""
+    from mashbox_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    N, D, taps = 5, 72, 4
+    w1, w2 = (1 + 0.1 * torch.randn(D, generator=g)).to(DEV), (1 + 0.1 * torch.randn(D, generator=g)).to(DEV)
+    cw = torch.randn(taps, D, generator=g).to(DEV)
+    slots = [4, 0, 2, 5, 1]
+    states = [torch.zeros(7, 16 + (taps - 1) * D, device=DEV) for _ in range(2)]
+    views = [s[:, 16:] for s in states]
+    xs = [torch.randn(N, D, generator=g).to(DEV).clone() for _ in range(2)]
+    xs[1].copy_(xs[0])
+    for step in range(6):                                                 # the state fills up and then shifts
+        d1, d2 = (torch.randn(N, D, generator=g).to(TD[dtype]).to(DEV) for _ in range(2))
+        a0, b0, a1, b1, c0 = (torch.empty(N, D, device=DEV, dtype=TD[dtype]) for _ in range(5))
+        ops.add_rmsnorm_pair(xs[0], d1, d2, w1, w2, 1e-5, a0, b0)
+        ops.short_conv(a0, cw, views[0], seq_arrays([1] * N, slots), c0, True)
+        ops.add_rmsnorm_pair_conv(xs[1], d1, d2, w1, w2, 1e-5, a1, b1, cw, views[1], i32(slots))
+        assert torch.equal(c0, a1) and torch.equal(b0, b1) and torch.equal(xs[0], xs[1]), f"step {step}"
+        assert torch.equal(states[0], states[1]), f"state after step {step}"
+
+
 class DiffCase:
     """S sequences with two-map queries and keys in shuffled pages; the step's queries are each sequence's last ones"""
 
@@ -203,6 +227,16 @@ DIFF_SHAPES = [  # lengths, query counts, H, G, dim, vdim, page, block of positi
     ((300, 130), (172, 1), 2, 1, 64, 128, 16, 128),
     ((700, 300, 9), (700, 260, 9), 4, 2, 32, 64, 16, 256),
     ((1000, 40), (1000, 33), 8, 2, 64, 128, 32, None),
+    # three query heads per kv head, pages of 8 and of 64; head sizes with swizzles of their own (16, 32) and the padded
+    # ones (48, 80, 96, 112); the widest pair
+    ((333, 150, 5), (333, 5, 5), 6, 2, 32, 64, 8, 96),
+    ((260, 77), (260, 3), 3, 1, 64, 128, 64, 128),
+    ((150, 70, 21), (150, 1, 4), 4, 2, 16, 32, 16, 48),
+    ((150, 70, 21), (150, 1, 4), 2, 1, 48, 96, 16, 64),
+    ((150, 70, 21), (150, 1, 4), 2, 2, 80, 112, 16, 100),
+    ((200, 90), (200, 2), 2, 1, 128, 128, 16, None),
+    ((130, 66), (130, 1), 2, 1, 16, 128, 16, 64),
+    ((130, 66), (130, 1), 2, 1, 128, 16, 16, 64),
 ]
 
 
