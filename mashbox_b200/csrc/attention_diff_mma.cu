@@ -559,19 +559,36 @@ __global__ void __launch_bounds__(THREADS) attn_diff_merge_kernel(const DiffPara
 #pragma unroll
         for (int m = 0; m < 2; m++) {
             const size_t base0 = (((size_t)slot * P.G + g) * MAX_SPLITS * 2 + m) * DBM + row;     // + split * 2 * DBM
+            // every split's maximum and weight first (loads that do not wait for one another), then the sums, four
+            // splits' loads in flight at a time, added in the order of the splits
+            float ms[MAX_SPLITS], ls[MAX_SPLITS];
             float M = -INFINITY, L = 0.0f;
-            for (int s = 0; s < n_splits; s++) M = fmaxf(M, part_ml[(base0 + (size_t)s * 2 * DBM) * 2]);
+#pragma unroll
+            for (int s = 0; s < MAX_SPLITS; s++) {
+                const float2 v = s < n_splits ? *reinterpret_cast<const float2*>(part_ml + (base0 + (size_t)s * 2 * DBM) * 2)
+                                              : make_float2(-INFINITY, 0.0f);
+                ms[s] = v.x; ls[s] = v.y;
+                M = fmaxf(M, v.x);
+            }
 #pragma unroll
             for (int i = 0; i < NC; i++) acc[m][i] = 0.0f;
-            for (int s = 0; s < n_splits; s++) {
-                const size_t base = base0 + (size_t)s * 2 * DBM;
-                const float ms = part_ml[base * 2];
-                const float f = ms == -INFINITY ? 0.0f : exp2f(ms - M);
-                L = fmaf(part_ml[base * 2 + 1], f, L);
 #pragma unroll
-                for (int i = 0; i < NC; i++) {
-                    const int d = lane + 32 * i;
-                    if (d < VD) acc[m][i] = fmaf(part_o[base * VD + d], f, acc[m][i]);
+            for (int s0 = 0; s0 < MAX_SPLITS; s0 += 4) {
+                if (s0 >= n_splits) break;
+                float v[4][NC];
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+#pragma unroll
+                    for (int i = 0; i < NC; i++) {
+                        const int d = lane + 32 * i;
+                        v[j][i] = (s0 + j < n_splits && d < VD) ? part_o[(base0 + (size_t)(s0 + j) * 2 * DBM) * VD + d] : 0.0f;
+                    }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float f = ms[s0 + j] == -INFINITY ? 0.0f : exp2f(ms[s0 + j] - M);
+                    L = fmaf(ls[s0 + j], f, L);
+#pragma unroll
+                    for (int i = 0; i < NC; i++) acc[m][i] = fmaf(v[j][i], f, acc[m][i]);
                 }
             }
             const float inv = L > 0.0f ? 1.0f / L : 0.0f;
