@@ -1,10 +1,10 @@
 """Typed configuration of the Luzosun decoder, read from config.json's own keys.
 
 config.json: `architecture` (a string), `width`, `vocab`, `embedding.scale`, `norm.eps`, `canon.taps` (the input
-convolution of every layer's mixer; absent or below 2: none) and `layers`, a list with one entry per layer: `type`
+convolution of every layer's mixer; absent: none; 1 is a filter of one tap, which keeps no state) and `layers`, a list with one entry per layer: `type`
 (the mixer kind; "attention" is the differential attention mixer), `mixer` (its sizes and constants) and `mlp`
 ({"kind": "dense", "ff": F} or null).  Every layer has its own sizes; nothing is assumed equal between layers.  A
-mixer entry: heads, kv_heads, dim (per map), vdim, conv (taps of the q/k/v convolutions), diff, scale, mask.size (the
+mixer entry: heads, kv_heads, dim (per map), vdim, conv (taps of the q/k/v convolutions; absent: none), diff, scale, mask.size (the
 block of positions a query sees; absent: all earlier keys), rot {base, dims, scaling.factor} (absent: no rotation),
 kv_from (the layer whose keys and values this one reads instead of making its own).
 """
@@ -22,7 +22,7 @@ class LuzosunMixer:
     vdim: int
     diff: float
     scale: float
-    conv: int = 1
+    conv: Optional[int] = None         # taps of the q/k/v convolutions; None: the mixer has none
     mask_size: Optional[int] = None
     rot_base: Optional[float] = None
     rot_dims: int = 0
@@ -93,7 +93,8 @@ class LuzosunConfig:
             mask = m.get("mask") or {}
             layers.append(LuzosunLayer(kind, LuzosunMixer(
                 heads=heads, kv_heads=kv, dim=dim, vdim=int(need(m, "vdim", w)), diff=float(need(m, "diff", w)),
-                scale=float(m["scale"]) if m.get("scale") is not None else dim ** -0.5, conv=int(m.get("conv") or 1),
+                scale=float(m["scale"]) if m.get("scale") is not None else dim ** -0.5,
+                conv=int(m["conv"]) if m.get("conv") else None,
                 mask_size=int(mask["size"]) if mask.get("size") else None,
                 rot_base=float(need(rot, "base", w + "rot.")) if rot else None, rot_dims=rot_dims,
                 rot_factor=float(rot["scaling"]["factor"]) if rot and (rot.get("scaling") or {}).get("factor") else None,
@@ -113,7 +114,9 @@ class LuzosunConfig:
         for layer in self.layers:
             m = layer.mixer
             e = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "diff": m.diff,
-                 "scale": m.scale, "conv": m.conv}
+                 "scale": m.scale}
+            if m.conv:
+                e["conv"] = m.conv
             if m.mask_size:
                 e["mask"] = {"size": m.mask_size}
             if m.rot_base is not None:

@@ -32,7 +32,7 @@ def model_spec(c: LuzosunConfig) -> ModelSpec:
         if layer.ff:
             ffn = PartSpec("dense_xielu", hidden=D, intermediate=layer.ff,
                            names=dict(up="mlp.up", down="mlp.down", act="mlp.act"))
-        conv = PartSpec("short", channels=D, taps=c.canon_taps, residual=True) if c.canon_taps > 1 else None
+        conv = PartSpec("short", channels=D, taps=c.canon_taps, residual=True) if c.canon_taps >= 1 else None
         layers.append(LayerSpec(prefix=f"l{i}.", block=PartSpec("parallel", mixer=mixer, ffn=ffn, norm1=norm,
                                                                  mixer_conv=conv)))
         own = m.kv_from is None
@@ -68,7 +68,7 @@ def stored_tensors(c: LuzosunConfig):
         for r, n in rows.items():
             out[p + "mix." + r] = ((n, D), "matrix")
             out[p + "mix." + r + ".b"] = ((n,), "bias")
-            if m.conv > 1:
+            if m.conv:
                 out[p + "mix." + r + ".conv"] = ((n, m.conv), "matrix")
         for v in ("lq1", "lk1", "lq2", "lk2"):
             out[p + "mix." + v] = ((m.dim,), "bias")
@@ -78,7 +78,7 @@ def stored_tensors(c: LuzosunConfig):
             out[p + "mlp.up"] = ((layer.ff, D), "matrix")
             out[p + "mlp.down"] = ((D, layer.ff), "matrix")
             out[p + "mlp.act"] = ((2,), "bias")
-        if c.canon_taps > 1:
+        if c.canon_taps >= 1:
             out[p + "canon1"] = ((D, c.canon_taps), "matrix")
     out["final.norm"] = ((D,), "norm")
     out["head"] = ((c.vocab, D), "matrix")

@@ -75,14 +75,16 @@ class DifferentialAttention:
         """forward() depends on the batch only through the lengths of the step's arrays; so must the position encoding"""
         return self.position is None or bool(getattr(self.position, "graph_safe", False))
 
-    def __init__(self, hidden, heads, kv_heads, dim, vdim, delta, eps, scale=None, bias=True, taps=1, position=None,
+    def __init__(self, hidden, heads, kv_heads, dim, vdim, delta, eps, scale=None, bias=True, taps=None, position=None,
                  chunk=None, shares_kv=False, prefix="", names=None):
         self.D, self.H, self.G, self.dim, self.vdim = int(hidden), int(heads), int(kv_heads), int(dim), int(vdim)
         if self.G < 1 or self.H % self.G:
             raise ConfigError(f"{heads} heads do not divide into {kv_heads} kv heads")
         self.delta, self.eps = float(delta), float(eps)
         self.scale = float(scale) if scale else self.dim ** -0.5
-        self.bias, self.taps = bool(bias), max(1, int(taps or 1))
+        self.bias = bool(bias)
+        self.has_conv = bool(taps)              # taps None or 0: no convolution; 1: a filter of one tap, no state
+        self.taps = int(taps) if taps else 1
         self.chunk = int(chunk) if chunk else None
         self.shares_kv = bool(shares_kv)
         n = dict(q="q", k="k", v="v", o="o", bias=".b", conv=".conv", lq1="lq1", lk1="lk1", lq2="lq2", lk2="lk2")
@@ -102,7 +104,7 @@ class DifferentialAttention:
             out.append(Want(self.n[r], (self.rows[r], self.D), "matrix"))
             if self.bias:
                 out.append(Want(self.n[r] + self.n["bias"], (self.rows[r],), "vector"))
-            if self.taps > 1:
+            if self.has_conv:
                 out.append(Want(self.n[r] + self.n["conv"], (self.rows[r], self.taps), "vector"))
         out += [Want(self.n[v], (self.dim,), "vector") for v in ("lq1", "lk1", "lq2", "lk2")]
         out.append(Want(self.n["o"], (self.D, self.H * self.vdim), "matrix"))
@@ -113,7 +115,7 @@ class DifferentialAttention:
         cat = lambda suffix: torch.cat([tensors[self.n[r] + suffix] for r in self.roles], 0).contiguous()
         self.w = cat("")
         self.b = cat(self.n["bias"]) if self.bias else None
-        self.wconv = cat(self.n["conv"]).t().contiguous() if self.taps > 1 else None      # (taps, channels)
+        self.wconv = cat(self.n["conv"]).t().contiguous() if self.has_conv else None      # (taps, channels)
         self.wo = tensors[self.n["o"]]
         dot = lambda a, b: float((tensors[self.n[a]].double() * tensors[self.n[b]].double()).sum())
         self.lam = math.exp(dot("lq1", "lk1")) - math.exp(dot("lq2", "lk2")) + self.delta

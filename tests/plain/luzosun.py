@@ -107,11 +107,11 @@ def feed_forward(b, W, p):
 
 
 def projections(a, W, p, names, taps):
-    """W a + bias, then (when the mixer has filters: taps > 1) the causal convolution of every channel"""
+    """W a + bias, then (when the mixer has filters: `taps` given) the causal convolution of every channel"""
     out = {}
     for n in names:
         u = a @ W[p + "mix." + n].T + W[p + "mix." + n + ".b"]
-        out[n] = causal_conv(u, W[p + "mix." + n + ".conv"]) if taps > 1 else u
+        out[n] = causal_conv(u, W[p + "mix." + n + ".conv"]) if taps else u
     return out
 
 
@@ -125,7 +125,7 @@ def attention_mixer(a, W, p, m, eps, positions, shared):
     if rot:
         freqs = rotary_frequencies(rot["base"], rot["dims"], (rot.get("scaling") or {}).get("factor"))
     own = m.get("kv_from") is None
-    pr = projections(a, W, p, ("q", "k", "v") if own else ("q",), int(m.get("conv") or 1))
+    pr = projections(a, W, p, ("q", "k", "v") if own else ("q",), m.get("conv"))
     q = pr["q"].reshape(T, H * 2, d)
     if freqs is not None:
         q = rotate_halves(q, positions, freqs)
@@ -154,7 +154,7 @@ def forward(cfg, W, tokens, layers_out=None):
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
         a = rms(x, eps, W[p + "norm1"])
-        if int((cfg.get("canon") or {}).get("taps") or 0) > 1:
+        if (cfg.get("canon") or {}).get("taps"):
             a = a + causal_conv(a, W[p + "canon1"])
         if layer["type"] != "attention":
             raise ValueError(layer["type"])

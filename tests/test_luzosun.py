@@ -46,6 +46,23 @@ def test_schedule_caches_and_state():
     assert states[3].shape == (1 * D + 4 * (2 * 48),)
 
 
+def test_filters_of_one_tap_and_no_filters():
+    """a convolution of one tap exists (its tensor is read) and keeps no state; an absent one has no tensor"""
+    cfg = L.LUZ_S
+    entry, back = read_config(cfg.to_hf())
+    assert back == cfg and "conv" not in cfg.to_hf()["layers"][0]["mixer"] and cfg.to_hf()["canon"] == {"taps": 1}
+    model = Model(entry.model_spec(cfg), cfg)
+    wants = {w.name: tuple(w.shape) for w in model.wants()}
+    assert wants["l0.canon1"] == (40, 1) and "l0.mix.q.conv" not in wants and wants["l1.mix.q.conv"] == (2 * 2 * 8, 2)
+    needs, states = model.cache_needs()
+    assert 0 not in states and states[1].shape == (1 * 2 * 2 * 8,)          # layer 0 carries nothing, layer 1 its q rows
+    assert needs[0].kind == "full"                                           # blocks of 3 and of 7: every position is kept
+    q = L.LUZ_Q
+    entry, back = read_config(q.to_hf())
+    assert back == q and back.layers[2].mixer.conv == 1 and back.layers[2].mixer.mask_size == 1 and back.layers[2].mixer.diff == 0.0
+    assert back.layers[0].mixer.conv is None and back.canon_taps == 0
+
+
 def test_config_refusals():
     good = L.LUZ_P.to_hf()
     for change, word in ((lambda c: c["layers"][1]["mixer"].update(kv_from=1), "kv_from"),

@@ -415,8 +415,12 @@ def test_unequal_requests_side_by_side_with_pages_and_slots_used_again(tmp_path_
 def test_long_decoding_with_a_small_pool(tmp_path_factory, name, dtype):
     """a short prompt and 400 tokens one by one in a pool that holds them only because blocks that were left give
     their pages back (configurations whose every cache has a mask); two requests side by side, one a block ahead"""
+    from mashbox_b200.config.registry import read_config
+    from mashbox_b200.models.model import Model
     cfg = L.CONFIGS[name][0]
-    masked = all(layer.mixer.mask_size for layer in cfg.layers)
+    entry, _ = read_config(cfg.to_hf())
+    needs, _ = Model(entry.model_spec(cfg), cfg).cache_needs()
+    masked = all(need.kind == "chunk" for need in needs.values())          # every cache gives left blocks back
     folder, runner = runner_for(tmp_path_factory.mktemp("m"), name, dtype, 448 if masked else 896)
     a, b = L.prompts_for(name, (412, 380), seed=4)
     steps = [dict(entries=[dict(id="a", tokens=a[:12], want=[11])], end=[]),
