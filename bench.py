@@ -652,14 +652,14 @@ def design_configs(size, layers, vocab=32000):
     from mashbox_b200.config.luzosun import LuzosunConfig, LuzosunLayer, LuzosunMixer
     z = DESIGN_SIZES[size]
     D, H, KV, dim = z["width"], z["heads"], z["kv_heads"], z["dim"]
-    own = LuzosunMixer(heads=H, kv_heads=KV, dim=dim, vdim=2 * dim, diff=0.3, scale=dim ** -0.5, conv=4,
-                       mask_size=z["block"], rot_base=20000.0, rot_dims=dim // 2, rot_factor=4.0)
+    own = LuzosunMixer(heads=H, kv_heads=KV, dim=dim, vdim=2 * dim, diff=0.25, scale=dim ** -0.5, conv=4,
+                       mask_size=z["block"], rot_base=10000.0, rot_dims=dim // 2, rot_factor=2.0)
     import dataclasses
     lz = LuzosunConfig("Luzosun", width=D, vocab=vocab, embedding_scale=1.0, norm_eps=1e-6, canon_taps=4, layers=tuple(
         LuzosunLayer("attention", own if i % 2 == 0 else dataclasses.replace(own, kv_from=i - 1), z["ff"] * 3 // 2)
         for i in range(layers)))
     ll = LlamaConfig(architecture="LlamaForCausalLM", num_layers=layers, hidden=D, num_heads=H, num_kv_heads=KV,
-                     head_dim=2 * dim, intermediate=z["ff"], vocab=vocab, rms_eps=1e-6, rope_theta=20000.0,
+                     head_dim=2 * dim, intermediate=z["ff"], vocab=vocab, rms_eps=1e-6, rope_theta=10000.0,
                      rope_scaling=None, tie_embeddings=False, attention_bias=True, max_position=131072)
     return lz, ll
 

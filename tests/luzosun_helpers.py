@@ -29,16 +29,16 @@ LUZ_P = LuzosunConfig("Luzosun", width=64, vocab=211, embedding_scale=4.0, norm_
 #    tap in another (they keep no state), no input convolution, one kv head, embedding scale 1
 LUZ_Q = LuzosunConfig("Luzosun", width=96, vocab=130, embedding_scale=1.0, norm_eps=1e-6, canon_taps=0, layers=(
     LuzosunLayer("attention", mixer(4, 1, 32, 32, 0.5, None, None, None), 128),
-    LuzosunLayer("attention", mixer(4, 4, 16, 48, 0.2, 4, 32, (20000.0, 16, 4.0)), 64),
+    LuzosunLayer("attention", mixer(4, 4, 16, 48, 0.2, 4, 32, (30000.0, 16, 2.0)), 64),
     LuzosunLayer("attention", mixer(2, 2, 16, 32, 0.0, 1, 1, (100.0, 16, None)), 40)))
 # R: head sizes the tensor-core attention kernel takes (multiples of 16), blocks of 64 and 128 positions
 # S: an input convolution of ONE tap (no state at all in a layer whose mixer has no filters), a mask of 3 positions
 LUZ_S = LuzosunConfig("Luzosun", width=40, vocab=97, embedding_scale=2.5, norm_eps=1e-5, canon_taps=1, layers=(
-    LuzosunLayer("attention", mixer(2, 1, 8, 24, 0.3, None, 3, (10000.0, 4, None)), 48),
+    LuzosunLayer("attention", mixer(2, 1, 8, 24, 0.45, None, 3, (10000.0, 4, None)), 48),
     LuzosunLayer("attention", mixer(2, 1, 8, 24, 0.6, 2, 7, (10000.0, 4, None), kv_from=0), None)))
-LUZ_R = LuzosunConfig("Luzosun", width=128, vocab=301, embedding_scale=8.0, norm_eps=1e-6, canon_taps=4, layers=(
-    LuzosunLayer("attention", mixer(4, 2, 32, 64, 0.3, 4, 64, (20000.0, 16, 4.0)), 192),
-    LuzosunLayer("attention", mixer(4, 2, 32, 64, 0.3, 4, 128, (20000.0, 16, 4.0), kv_from=0), 192),
+LUZ_R = LuzosunConfig("Luzosun", width=128, vocab=301, embedding_scale=8.0, norm_eps=2e-6, canon_taps=3, layers=(
+    LuzosunLayer("attention", mixer(4, 2, 32, 64, 0.35, 5, 64, (50000.0, 16, 8.0)), 192),
+    LuzosunLayer("attention", mixer(4, 2, 32, 64, 0.25, 2, 128, (50000.0, 16, 8.0), kv_from=0), 192),
     LuzosunLayer("attention", mixer(2, 1, 64, 128, 0.2, 3, 64, (1000.0, 64, None)), 96)))
 CONFIGS = {"P": (LUZ_P, 5, 8), "Q": (LUZ_Q, 6, 16), "R": (LUZ_R, 7, 16), "S": (LUZ_S, 8, 4)}       # config, seed, page size
 

@@ -146,7 +146,7 @@ def test_plain_activation_and_rotation():
 
 def test_rotary_part_divides_by_the_factor():
     from mashbox_b200.parts.position import RotaryEncoding
-    for base, dims, factor in ((20000.0, 24, 4.0), (10000.0, 8, 3.0), (500.0, 64, None)):
+    for base, dims, factor in ((30000.0, 40, 2.0), (10000.0, 8, 3.0), (500.0, 64, None)):
         part = RotaryEncoding(head_dim=dims + 8, rotary_dim=dims, theta=base, pairing="halves",
                               scaling=("divide", factor) if factor else None)
         assert np.allclose(part.frequencies(), plain.rotary_frequencies(base, dims, factor), rtol=3e-7, atol=0)

@@ -232,7 +232,7 @@ DIFF_SHAPES = [  # lengths, query counts, H, G, dim, vdim, page, block of positi
     ((333, 150, 5), (333, 5, 5), 6, 2, 32, 64, 8, 96),
     ((260, 77), (260, 3), 3, 1, 64, 128, 64, 128),
     ((150, 70, 21), (150, 1, 4), 4, 2, 16, 32, 16, 48),
-    ((150, 70, 21), (150, 1, 4), 2, 1, 48, 96, 16, 64),
+    ((150, 70, 21), (150, 1, 4), 2, 1, 48, 112, 16, 72),
     ((150, 70, 21), (150, 1, 4), 2, 2, 80, 112, 16, 100),
     ((200, 90), (200, 2), 2, 1, 128, 128, 16, None),
     ((130, 66), (130, 1), 2, 1, 16, 128, 16, 64),
@@ -253,7 +253,7 @@ def kernels_for(dtype, dim, vdim, page=16):
 def test_differential_attention_kernels(dtype, shape):
     lengths, q_lens, H, G, dim, vdim, page, chunk = shape
     case = DiffCase(lengths, q_lens, H, G, dim, vdim, page, dtype, seed=len(lengths)).build()
-    scale, lam, delta, eps = dim ** -0.5, 0.37, 0.3, 1e-5
+    scale, lam, delta, eps = dim ** -0.5, 0.37, 0.28, 1e-5
     want = case.reference(scale, chunk, lam, delta, eps)
     for kernel in kernels_for(dtype, dim, vdim, page):
         kernel_close(run_diff(case, chunk, scale, lam, delta, eps, kernel), want, dtype, f"{kernel} kernel, {shape}")
