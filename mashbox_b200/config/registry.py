@@ -53,9 +53,13 @@ def _builtin():
     if _done:
         return
     _done = True
-    from ..models import llama, luzosun
+    from ..models import llama, luzosun, sufopel
     from .llama import LlamaConfig
     from .luzosun import LuzosunConfig
+    from .sufopel import SufopelConfig
+    if "Sufopel" not in ARCHITECTURES:
+        register_architecture(Architecture("Sufopel", SufopelConfig, sufopel.model_spec, sufopel.canonical_names,
+                                           sufopel.stored_tensors))
     if "Luzosun" not in ARCHITECTURES:
         register_architecture(Architecture("Luzosun", LuzosunConfig, luzosun.model_spec, luzosun.canonical_names,
                                            luzosun.stored_tensors))

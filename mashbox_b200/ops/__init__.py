@@ -19,7 +19,8 @@ torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 torch.backends.cuda.matmul.allow_tf32 = False
 
 DEVICE_ERRORS = {1: "a token id outside the vocabulary", 2: "a position whose cache page the block table does not hold",
-                 3: "a page id outside the cache pool", 4: "a bounded wait inside a kernel ran out"}
+                 3: "a page id outside the cache pool", 4: "a bounded wait inside a kernel ran out",
+                 5: "a position outside the learned position table"}
 
 
 def _suffix(dtype):
@@ -266,6 +267,163 @@ def swiglu(gu, out):
     N, F = out.shape
     f = _fn("elementwise", "mb_swiglu_" + _suffix(out.dtype), [c_void_p, c_void_p, c_int, c_int, c_void_p])
     _check(f(_p(gu), _p(out), N, F, _stream()), "swiglu")
+
+
+# ------------------------------------------------------------------------------------------------ row-wise kernels
+c_ll = ctypes.c_longlong
+
+
+def embed_positions(tokens, positions, table, pos_table, x, err, scale=1.0):
+    """x[n] = table[tokens[n]] * scale + pos_table[positions[n]] into the float32 residual stream x (N, D)"""
+    _cuda(tokens, positions, table, pos_table, x)
+    N, D = x.shape
+    f = _fn("rowwise", "mb_embed_pos_" + _suffix(table.dtype),
+            [c_void_p] * 5 + [c_int] * 4 + [c_float, c_void_p, c_void_p])
+    _check(f(_p(tokens), _p(positions), _p(table), _p(pos_table), _p(x), N, D, table.shape[0], pos_table.shape[0],
+             float(scale), _p(err), _stream()), "embed_positions")
+
+
+def post_norm_add(x, delta, post_w, post_eps, next_w=None, next_eps=0.0, normed=None, copy=None):
+    """x (N, D) float32 += delta / sqrt(mean(delta^2) + post_eps) * post_w (delta in the activation dtype, post_w float32);
+    with next_w and normed: normed = x / sqrt(mean(x^2) + next_eps) * next_w; copy: x in the activation dtype"""
+    _cuda(x, delta, post_w, next_w, normed, copy)
+    N, D = x.shape
+    f = _fn("rowwise", "mb_post_norm_add_" + _suffix(delta.dtype),
+            [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_p(x), _p(delta), _p(post_w), float(post_eps), _p(next_w), float(next_eps), _p(normed), _p(copy), N, D,
+             _stream()), "post_norm_add")
+
+
+def rms_segments(rows, off_a, w_a, out_a, off_b, w_b, pool, positions, tok_row, table, page, num_pages, eps, err):
+    """Two stretches of columns of rows (N, C), each divided by its root mean square and multiplied by a weight of its
+    own: columns off_a .. off_a + len(w_a) go to out_a (N, len(w_a)); columns off_b .. off_b + len(w_b) go into pool
+    (pages, 1, page, len(w_b)) at the page and slot of the token's position (w_b None: no second stretch)."""
+    _cuda(rows, w_a, out_a, w_b, pool, positions, tok_row, table)
+    N, C = rows.shape
+    wa = 0 if w_a is None else w_a.shape[0]
+    wb = 0 if w_b is None else w_b.shape[0]
+    f = _fn("rowwise", "mb_rms_segments_" + _suffix(rows.dtype),
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
+    _check(f(_p(rows), rows.stride(0), off_a, wa, _p(w_a), _p(out_a), off_b, wb, _p(w_b), _p(pool), _p(positions),
+             _p(tok_row), _p(table), table.shape[1] if table is not None else 0, page, num_pages, float(eps), N, _p(err),
+             _stream()), "rms_segments")
+
+
+def gated_gather(z, tokens, table, off, out, err):
+    """out[n, j] = gelu_tanh(z[n, j]) * table[tokens[n], off + j]; z, out (N, W), table (V, any) in the activation dtype"""
+    _cuda(z, tokens, table, out)
+    N, W = z.shape
+    f = _fn("rowwise", "mb_gated_gather_" + _suffix(z.dtype),
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_p(z), _p(tokens), _p(table), table.stride(0), int(off), _p(out), N, W, table.shape[0], _p(err), _stream()),
+           "gated_gather")
+
+
+def sigmoid_mul(o, gate):
+    """o (N, C) *= sigmoid(gate), in place; gate a view (N, C) whose rows may be further apart than C"""
+    _cuda(o, gate)
+    N, C = o.shape
+    if gate.stride(1) != 1:
+        raise KernelError("sigmoid_mul: the gate's columns must be contiguous")
+    f = _fn("rowwise", "mb_sigmoid_mul_" + _suffix(o.dtype), [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_p(o), _p(gate), gate.stride(0), N, C, _stream()), "sigmoid_mul")
+
+
+# The per-head products run on the package's plain kernel up to this many tokens (and always in float32); larger bf16
+# steps hand them to the library's batched product.
+HEAD_PRODUCT = {"tokens": 32}
+
+
+def head_product(x, w, out, heads, transposed):
+    """A projection applied head by head.  x (N, heads * I), out (N, heads * J), w the stored matrix:
+    transposed=False: w (heads * J, I) and out[n, h] = w[h] x[n, h] (rows of a head side by side);
+    transposed=True:  w (heads * I, J) and out[n, h] = w[h]^T x[n, h] (the same matrix applied from the other side)."""
+    _cuda(x, w, out)
+    N = x.shape[0]
+    I, J = x.shape[1] // heads, out.shape[1] // heads
+    if tuple(w.shape) != ((heads * I, J) if transposed else (heads * J, I)) or not w.is_contiguous():
+        raise KernelError("head_product: the matrix does not fit the heads")
+    if x.dtype == torch.bfloat16 and N > HEAD_PRODUCT["tokens"]:
+        a = x.view(N, heads, I).transpose(0, 1)
+        b = w.view(heads, I, J) if transposed else w.view(heads, J, I).transpose(1, 2)
+        out.view(N, heads, J).copy_(torch.bmm(a, b).transpose(0, 1))
+        return out
+    sh, si, sj = (I * J, J, 1) if transposed else (I * J, 1, I)
+    f = _fn("rowwise", "mb_head_product_" + _suffix(x.dtype),
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_void_p])
+    _check(f(_p(x), _p(w), _p(out), N, heads, I, J, sh, si, sj, _stream()), "head_product")
+    return out
+
+
+def scale_rows(y, s):
+    """y (float32) *= s, in place"""
+    _cuda(y)
+    f = _fn("rowwise", "mb_scale_rows", [c_void_p, c_float, c_ll, c_void_p])
+    _check(f(_p(y), float(s), y.numel(), _stream()), "scale_rows")
+
+
+# ------------------------------------------------------------------------------------------------ gated delta rule
+def delta_gates(qkv, low, wide, A_log, dt_bias, q, k, v, g, beta, H, G, dim, vdim, unit_eps=1e-6):
+    """What the delta rule reads, in float32, from a layer's products.  qkv (N, 2 G dim + H vdim) = [q | k | v] (after
+    their convolutions): silu; q, k to unit vectors per head, x / sqrt(sum x^2 + unit_eps), q also times dim^-1/2.
+    low (N, >= H): beta = sigmoid of its first H columns.  wide (N, H dim + H vdim): g = exp(-exp(A_log[h])
+    softplus(wide[:, :H dim] + dt_bias)).  Outputs q, k (N, G dim), v (N, H vdim), g (N, H dim), beta (N, H)."""
+    _cuda(qkv, low, wide, A_log, dt_bias, q, k, v, g, beta)
+    f = _fn("delta_rule", "mb_delta_gates_" + _suffix(qkv.dtype),
+            [c_void_p, c_void_p, c_int] + [c_void_p] * 8 + [c_int] * 5 + [c_float, c_void_p])
+    _check(f(_p(qkv), _p(low), low.stride(0), _p(wide), _p(A_log), _p(dt_bias), _p(q), _p(k), _p(v), _p(g), _p(beta),
+             qkv.shape[0], H, G, dim, vdim, float(unit_eps), _stream()), "delta_gates")
+
+
+def delta_rule(q, k, v, g, beta, o, state, seq, H, G, dim, vdim):
+    """Per sequence and head, token by token: S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
+    q, k (N, G dim), v, o (N, H vdim), g (N, H dim), beta (N, H), all float32; state (slots, H dim vdim) float32 (a view,
+    slots state.stride(0) apart), read at the start of each sequence's stretch and replaced at its end.
+    seq = (q_start, q_len, state_slot) int32 device arrays, one entry per sequence of the step."""
+    _cuda(q, k, v, g, beta, o, state, *seq)
+    f = _fn("delta_rule", "mb_delta_rule", [c_void_p] * 7 + [c_ll] + [c_void_p] * 3 + [c_int] * 5 + [c_void_p])
+    _check(f(_p(q), _p(k), _p(v), _p(g), _p(beta), _p(o), _p(state), state.stride(0), _p(seq[0]), _p(seq[1]), _p(seq[2]),
+             seq[0].shape[0], H, G, dim, vdim, _stream()), "delta_rule")
+
+
+def gated_rms(o, gate, w, out, H, vdim, eps):
+    """out[n, h] = o[n, h] / sqrt(mean(o[n, h]^2) + eps) * w * sigmoid(gate[n, h]); o (N, H vdim) float32, gate a view
+    (N, H vdim) of the activation dtype whose rows may be further apart, w (vdim,) float32, out the activation dtype"""
+    _cuda(o, gate, w, out)
+    f = _fn("delta_rule", "mb_gated_rms_" + _suffix(out.dtype),
+            [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_p(o), _p(gate), gate.stride(0), 0, _p(w), _p(out), o.shape[0], H, vdim, float(eps), _stream()), "gated_rms")
+
+
+# ------------------------------------------------------------------------------------------------ routed experts
+def moe_select(z, correction, ids, wts, groups=1, keep=1):
+    """z (N, E) float32 router logits -> ids (N, top) int32, wts (N, top) float32: scores sigmoid(z); chosen by score +
+    correction among the experts of the `keep` best of `groups` runs of neighbours (a run's worth: its two largest);
+    the weights are the chosen experts' scores"""
+    _cuda(z, correction, ids, wts)
+    N, E = z.shape
+    f = _fn("moe", "mb_moe_select", [c_void_p] * 4 + [c_int] * 5 + [c_void_p])
+    _check(f(_p(z), _p(correction), _p(ids), _p(wts), N, E, ids.shape[1], int(groups), int(keep), _stream()), "moe_select")
+
+
+def moe_experts(h, ids, wg, wu, wd, y, limit, alpha):
+    """y[n, k] = Wd[e] (g sigmoid(alpha g) (u + 1)), g = min(Wg[e] h[n], limit), u = clamp(Wu[e] h[n], -limit, limit),
+    e = ids[n, k].  h (N, D); wg, wu (E, F, D); wd (E, D, F); y (N, top, D) float32"""
+    _cuda(h, ids, wg, wu, wd, y)
+    N, D = h.shape
+    E, F, _ = wg.shape
+    f = _fn("moe", "mb_moe_experts_" + _suffix(h.dtype), [c_void_p] * 6 + [c_int] * 5 + [c_float, c_float, c_void_p])
+    _check(f(_p(h), _p(ids), _p(wg), _p(wu), _p(wd), _p(y), N, D, F, E, ids.shape[1], float(limit), float(alpha),
+             _stream()), "moe_experts")
+
+
+def moe_combine(y, wts, out):
+    """out[n] = sum_k wts[n, k] y[n, k] (places in order); y (N, top, D) float32, out (N, D) the activation dtype"""
+    _cuda(y, wts, out)
+    N, top, D = y.shape
+    f = _fn("moe", "mb_moe_combine_" + _suffix(out.dtype), [c_void_p] * 3 + [c_int] * 3 + [c_void_p])
+    _check(f(_p(y), _p(wts), _p(out), N, D, top, _stream()), "moe_combine")
 
 
 # ------------------------------------------------------------------------------------------------ contractions

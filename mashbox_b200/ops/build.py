@@ -35,6 +35,9 @@ LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "attention_diff_mma_64_128": ("attention_diff_mma.cu", ["-DDIFF_DIM=64", "-DDIFF_VD=128"]),
     "attention_diff_mma_128_128": ("attention_diff_mma.cu", ["-DDIFF_DIM=128", "-DDIFF_VD=128"]),
     "short_conv": ("short_conv.cu", []),
+    "rowwise": ("rowwise.cu", []),                                     # learned positions, norms of sublayer outputs, latents
+    "delta_rule": ("delta_rule.cu", []),                               # the gated delta rule and what feeds it
+    "moe": ("moe.cu", []),                                             # routed experts
     "attention_mma": ("attention_mma.cu", []),                         # head sizes 16, 32, 64, 128
     "attention_mma_wide": ("attention_mma.cu", ["-DMB_ATTN_WIDE"]),    # the other multiples of 16 up to 256
     "attention_tma": ("attention_tma.cu", []),

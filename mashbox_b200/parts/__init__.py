@@ -1,4 +1,5 @@
 """Parts a layer is put together from.  Importing this package registers the built-in kinds."""
-from . import base, norm, position, conv, attention, diff_attention, feed_forward, block, embedding  # noqa: F401
+from . import (base, norm, position, conv, attention, diff_attention, latent_attention, channel_delta,  # noqa: F401
+               feed_forward, routed_experts, token_side, block, embedding)
 from .base import (PartSpec, LayerSpec, LayerRun, ModelSpec, Env, StepContext, StepInputs, Workspace,  # noqa: F401
                    register, make)

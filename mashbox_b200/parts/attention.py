@@ -46,51 +46,18 @@ def many_splits(blocks, work, slots, head_dim, most=4):
     return 1 + next(i for i, c in enumerate(costs) if c <= 1.01 * best)
 
 
-class Attention:
-    @property
-    def graph_safe(self):
-        """forward() depends on the batch only through the lengths of the step's arrays; so must the position encoding"""
-        return self.position is None or bool(getattr(self.position, "graph_safe", False))
+class PagedAttention:
+    """Attention of a step's queries over rows kept per position in pages: the work lists (`prepare`, on the host) and
+    the choice of kernel (`attend`).  `heads` query heads read `kv_heads` rows of `head_dim` values per position;
+    whoever keeps other things per position than keys and values of its own (one latent vector that is key and value at
+    once, say) hands its pools in."""
 
-    def __init__(self, hidden, heads, kv_heads, head_dim, bias=False, position=None, window=None, scale=None,
-                 prefix="", names=None):
-        self.D, self.H, self.KV, self.HD = int(hidden), int(heads), int(kv_heads), int(head_dim)
+    def __init__(self, heads, kv_heads, head_dim, window=None, scale=None):
+        self.H, self.KV, self.HD = int(heads), int(kv_heads), int(head_dim)
         if self.H % self.KV:
             raise ConfigError(f"{heads} heads do not divide into {kv_heads} kv heads")
-        self.bias, self.window = bool(bias), (int(window) if window else None)
+        self.window = int(window) if window else None
         self.scale = float(scale) if scale else self.HD ** -0.5
-        self.prefix = prefix
-        n = dict(q="attn_q", k="attn_k", v="attn_v", o="attn_output")
-        n.update(names or {})
-        self.names = {k: prefix + v for k, v in n.items()}
-        self.position = make("position", position) if isinstance(position, PartSpec) else position
-        self.wqkv = self.bqkv = self.wo = self.bo = None
-
-    # ------------------------------------------------------------------------------------------ weights
-    def wants(self):
-        H, KV, HD, D = self.H, self.KV, self.HD, self.D
-        shapes = dict(q=(H * HD, D), k=(KV * HD, D), v=(KV * HD, D), o=(D, H * HD))
-        w = [Want(self.names[r] + ".weight", shapes[r], "matrix") for r in "qkvo"]
-        if self.bias:
-            w += [Want(self.names[r] + ".bias", (shapes[r][0],), "vector") for r in "qkvo"]
-        return w + (self.position.wants() if self.position is not None else [])
-
-    def bind(self, tensors, env):
-        import torch
-        t = lambda r, s: tensors[self.names[r] + s]
-        self.wqkv = torch.cat([t("q", ".weight"), t("k", ".weight"), t("v", ".weight")], 0).contiguous()
-        self.wo = t("o", ".weight")
-        if self.bias:
-            self.bqkv = torch.cat([t("q", ".bias"), t("k", ".bias"), t("v", ".bias")], 0).contiguous()
-            self.bo = t("o", ".bias")
-        if self.position is not None:
-            self.position.bind(tensors, env)
-
-    def cache_need(self):
-        return CacheNeed.keys_and_values(self.KV, self.HD, self.window)
-
-    def state_need(self):
-        return None
 
     # ------------------------------------------------------------------------------------------ planning
     def uses_mma(self, ctx):
@@ -201,6 +168,97 @@ class Attention:
         ctx.memo[key] = dict(name=name, n_dec=len(dec), n_pre=len(pre), n_part=len(part_tok) // 2,
                              max_splits=max_splits, tc5=tc5, cluster=cluster)
 
+    # ------------------------------------------------------------------------------------------ kernels
+    def attend(self, ctx, qkv, width, out, table, kpool, vpool, rope=None):
+        """The step's queries -- rows of qkv, `width` values apart, head h at column h * head_dim -- attend to the rows
+        of their sequences' pages; out (N, heads * head_dim).  rope = (bias, freqs, rotary dims, pairing): the decode
+        form of the TMA kernel rotates and stores the step's own keys and values from qkv itself."""
+        import torch
+        ops = ctx.ops
+        H, KV, HD = self.H, self.KV, self.HD
+        page, pages = ctx.cache.page_size, ctx.cache.pool_pages
+        if self.uses_mma(ctx):
+            plan = ctx.memo[self.plan_key()]
+            nm = plan["name"]
+            n_part, ms = plan["n_part"], plan["max_splits"]
+            part_o = part_ml = None
+            if n_part:
+                part_o = ctx.ws.get("attn_part_o", n_part * H * ms, (HD,), torch.float32, reserve=0)
+                part_ml = ctx.ws.get("attn_part_ml", n_part * H * ms, (2,), torch.float32, reserve=0)
+            kind = ctx.options.get("attention_kernel", "tma")
+            tma = kind == "tma" and ops.attention_tma_supports(HD, page)
+            flash = ops.attention_tma if tma else ops.attention_mma
+            # the TMA kernel merges the splits itself (the last block of a group does it); the other needs the merge kernel
+            fused = (tma and n_part > 0 and ctx.options.get("attention_fused_merge", True)
+                     and ops.attention_tma_merges(max(plan["n_pre"], plan["n_dec"]), KV))
+            extra = dict(merge=True) if fused else {}
+            if rope is not None:
+                extra["rope"] = rope
+            if plan["tc5"] and plan["n_pre"]:
+                ops.attention_tc5(qkv, width, out, kpool, vpool, ctx.dev(nm + "pre"), plan["n_pre"], ctx.dev("q_start"),
+                                  ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev("seq_row"), table, H, KV, HD, page, pages,
+                                  self.window, self.scale, ctx.err)
+            for form, n_items, decode in ((nm + "pre", 0 if plan["tc5"] else plan["n_pre"], False),
+                                          (nm + "dec", plan["n_dec"], True)):
+                if n_items and decode and plan["cluster"]:
+                    ops.attention_tma(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, True, ctx.dev("q_start"),
+                                      ctx.dev("q_len"), ctx.dev("pos0"), None, ctx.dev("seq_row"), table, None, None, 1,
+                                      H, KV, HD, page, pages, self.window, self.scale, ctx.err,
+                                      rope=extra.get("rope"), cluster=plan["cluster"])
+                elif n_items:
+                    flash(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, decode, ctx.dev("q_start"),
+                          ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev(nm + "part_base"), ctx.dev("seq_row"),
+                          table, part_o, part_ml, ms, H, KV, HD, page, pages, self.window, self.scale, ctx.err, **extra)
+            if n_part and not fused:
+                ops.attention_merge(part_o, part_ml, ctx.dev(nm + "part_tok"), n_part, out, H, HD, ms)
+        else:
+            ops.attention_simple(qkv, width, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, KV,
+                                 HD, page, pages, self.window, self.scale, ctx.err)
+
+
+class Attention(PagedAttention):
+    @property
+    def graph_safe(self):
+        """forward() depends on the batch only through the lengths of the step's arrays; so must the position encoding"""
+        return self.position is None or bool(getattr(self.position, "graph_safe", False))
+
+    def __init__(self, hidden, heads, kv_heads, head_dim, bias=False, position=None, window=None, scale=None,
+                 prefix="", names=None):
+        super().__init__(heads, kv_heads, head_dim, window, scale)
+        self.D, self.bias = int(hidden), bool(bias)
+        self.prefix = prefix
+        n = dict(q="attn_q", k="attn_k", v="attn_v", o="attn_output")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.position = make("position", position) if isinstance(position, PartSpec) else position
+        self.wqkv = self.bqkv = self.wo = self.bo = None
+
+    # ------------------------------------------------------------------------------------------ weights
+    def wants(self):
+        H, KV, HD, D = self.H, self.KV, self.HD, self.D
+        shapes = dict(q=(H * HD, D), k=(KV * HD, D), v=(KV * HD, D), o=(D, H * HD))
+        w = [Want(self.names[r] + ".weight", shapes[r], "matrix") for r in "qkvo"]
+        if self.bias:
+            w += [Want(self.names[r] + ".bias", (shapes[r][0],), "vector") for r in "qkvo"]
+        return w + (self.position.wants() if self.position is not None else [])
+
+    def bind(self, tensors, env):
+        import torch
+        t = lambda r, s: tensors[self.names[r] + s]
+        self.wqkv = torch.cat([t("q", ".weight"), t("k", ".weight"), t("v", ".weight")], 0).contiguous()
+        self.wo = t("o", ".weight")
+        if self.bias:
+            self.bqkv = torch.cat([t("q", ".bias"), t("k", ".bias"), t("v", ".bias")], 0).contiguous()
+            self.bo = t("o", ".bias")
+        if self.position is not None:
+            self.position.bind(tensors, env)
+
+    def cache_need(self):
+        return CacheNeed.keys_and_values(self.KV, self.HD, self.window)
+
+    def state_need(self):
+        return None
+
     # ------------------------------------------------------------------------------------------ forward
     fuses_small = True      # forward() takes normed= and residual= (see PreNormBlock)
 
@@ -251,43 +309,8 @@ class Attention:
                                   kpool if run.write else None, vpool if run.write else None, freqs, H, KV, HD, rd,
                                   pairing, page, pages, ctx.err)
         out = ctx.ws.get("attn_out", N, (H * HD,), ctx.dtype)
-        if self.uses_mma(ctx):
-            plan = ctx.memo[self.plan_key()]
-            nm = plan["name"]
-            n_part, ms = plan["n_part"], plan["max_splits"]
-            part_o = part_ml = None
-            if n_part:
-                part_o = ctx.ws.get("attn_part_o", n_part * H * ms, (HD,), torch.float32, reserve=0)
-                part_ml = ctx.ws.get("attn_part_ml", n_part * H * ms, (2,), torch.float32, reserve=0)
-            kind = ctx.options.get("attention_kernel", "tma")
-            tma = kind == "tma" and ops.attention_tma_supports(HD, page)
-            flash = ops.attention_tma if tma else ops.attention_mma
-            # the TMA kernel merges the splits itself (the last block of a group does it); the other needs the merge kernel
-            fused = (tma and n_part > 0 and ctx.options.get("attention_fused_merge", True)
-                     and ops.attention_tma_merges(max(plan["n_pre"], plan["n_dec"]), KV))
-            extra = dict(merge=True) if fused else {}
-            if folded:
-                extra["rope"] = (self.bqkv, freqs, rd, pairing)
-            if plan["tc5"] and plan["n_pre"]:
-                ops.attention_tc5(qkv, width, out, kpool, vpool, ctx.dev(nm + "pre"), plan["n_pre"], ctx.dev("q_start"),
-                                  ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev("seq_row"), table, H, KV, HD, page, pages,
-                                  self.window, self.scale, ctx.err)
-            for form, n_items, decode in ((nm + "pre", 0 if plan["tc5"] else plan["n_pre"], False),
-                                          (nm + "dec", plan["n_dec"], True)):
-                if n_items and decode and plan["cluster"]:
-                    ops.attention_tma(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, True, ctx.dev("q_start"),
-                                      ctx.dev("q_len"), ctx.dev("pos0"), None, ctx.dev("seq_row"), table, None, None, 1,
-                                      H, KV, HD, page, pages, self.window, self.scale, ctx.err,
-                                      rope=extra.get("rope"), cluster=plan["cluster"])
-                elif n_items:
-                    flash(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, decode, ctx.dev("q_start"),
-                          ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev(nm + "part_base"), ctx.dev("seq_row"),
-                          table, part_o, part_ml, ms, H, KV, HD, page, pages, self.window, self.scale, ctx.err, **extra)
-            if n_part and not fused:
-                ops.attention_merge(part_o, part_ml, ctx.dev(nm + "part_tok"), n_part, out, H, HD, ms)
-        else:
-            ops.attention_simple(qkv, width, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, KV,
-                                 HD, page, pages, self.window, self.scale, ctx.err)
+        self.attend(ctx, qkv, width, out, table, kpool, vpool,
+                    rope=(self.bqkv, freqs, rd, pairing) if folded else None)
         if residual is not None:
             ctx.add_into_stream(out, self.wo, residual, self.bo)
             return None

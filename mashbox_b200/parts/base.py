@@ -19,6 +19,8 @@ Interfaces (all tensors on the device; N = tokens of the step, D = the part's wi
   FeedForward   wants(prefix);  bind;  forward(ctx, h) -> (delta, bias or None)
   Conv          wants();  bind;  state_floats() -> float32 values it keeps per request (its layer's block gives it a
                 stretch of the layer's state: state_offset);  prepare(ctx);  forward(ctx, h, state_id) -> h'
+  Side          an input a layer takes from the token itself: wants();  bind;  forward(ctx, x, xa, next_norm, normed)
+                adds into the stream x (xa: the same rows in the activation dtype)
   Block         built from the part specs in its own PartSpec and the layer's prefix;  parts() -> every part it
                 holds;  mixer: the part that owns the cache of a run;  forward(ctx, x, pending, run) -> pending
 
@@ -94,13 +96,13 @@ class ModelSpec:
     head: PartSpec
 
 
-NORMS, POSITIONS, MIXERS, FEED_FORWARDS, BLOCKS, EMBEDDINGS, HEADS, CONVS = {}, {}, {}, {}, {}, {}, {}, {}
+NORMS, POSITIONS, MIXERS, FEED_FORWARDS, BLOCKS, EMBEDDINGS, HEADS, CONVS, SIDES = {}, {}, {}, {}, {}, {}, {}, {}, {}
 _TABLES = {"norm": NORMS, "position": POSITIONS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS, "block": BLOCKS,
-           "embedding": EMBEDDINGS, "head": HEADS, "conv": CONVS}
+           "embedding": EMBEDDINGS, "head": HEADS, "conv": CONVS, "side": SIDES}
 
 
 def register(family, kind, cls):
-    """Adds a part kind: family is norm | position | mixer | feed_forward | block | embedding | head | conv."""
+    """Adds a part kind: family is norm | position | mixer | feed_forward | block | embedding | head | conv | side."""
     _TABLES[family][kind] = cls
     return cls
 

@@ -3,6 +3,9 @@
 "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x)) (src/mashbox/gguf/archs/dense.py:339-357).  The adds are deferred: a
 sublayer returns its output as `pending` and the next norm adds it into the float32 residual stream in the same kernel
 that normalises, so the block returns the feed-forward's output still pending.
+
+"sandwich": a norm before AND after each sublayer, the normed output scaled per channel before it joins the stream,
+and optionally an input from the token itself at the layer's end (see SandwichBlock).
 """
 from ..errors import ConfigError
 from .base import make, register
@@ -124,3 +127,88 @@ class ParallelBlock:
 
 
 register("block", "parallel", ParallelBlock)
+
+
+class SandwichBlock:
+    """x += l1 * post1(mixer(pre1(x)));  x += l2 * post2(ffn(pre2(x)));  then, optionally, side(x, token) adds into x.
+
+    pre and post norms are RMS norms; l1, l2 (`scale1`, `scale2`: tensor names under the layer's prefix, or None) scale
+    the normed outputs channel by channel and are multiplied into the post norms' weights at load.  One kernel norms a
+    sublayer's output, adds it into the float32 stream and makes the norm that reads the stream next -- the
+    feed-forward's pre norm, or the first norm of the block that runs next -- so the stream is read once per sublayer.
+    `ffn` may be None (the layer has no feed-forward), `side` may be None.  Nothing is left pending."""
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
+
+    def __init__(self, prefix, mixer, norm, ffn=None, side=None, scale1=None, scale2=None, names=None):
+        n = dict(pre1="norm1", post1="norm1b", pre2="norm2", post2="norm2b")
+        n.update(names or {})
+        self.pre1 = make("norm", norm, name=prefix + n["pre1"])
+        self.post1 = make("norm", norm, name=prefix + n["post1"])
+        self.mixer = make("mixer", mixer, prefix=prefix)
+        self.ffn = make("feed_forward", ffn, prefix=prefix) if ffn is not None else None
+        self.pre2 = make("norm", norm, name=prefix + n["pre2"]) if self.ffn is not None else None
+        self.post2 = make("norm", norm, name=prefix + n["post2"]) if self.ffn is not None else None
+        self.side = make("side", side, prefix=prefix) if side is not None else None
+        self.scale_names = (prefix + scale1 if scale1 else None, prefix + scale2 if scale2 and self.ffn is not None else None)
+        self.width = self.pre1.width
+        self.post_w = [None, None]
+
+    def parts(self):
+        return [p for p in (self.pre1, self.mixer, self.post1, self.pre2, self.ffn, self.post2, self.side, self)
+                if p is not None]
+
+    # the block is a part of its own for the two scale vectors
+    def wants(self):
+        from ..weights.loader import Want
+        return [Want(n, (self.width,), "vector") for n in self.scale_names if n is not None]
+
+    def bind(self, tensors, env):
+        for i, (post, name) in enumerate(zip((self.post1, self.post2), self.scale_names)):
+            if post is not None:
+                self.post_w[i] = post.weight * tensors[name] if name is not None else post.weight
+
+    def first_norm(self):
+        return self.pre1
+
+    def state_need(self):
+        return self.mixer.state_need()
+
+    def prepare(self, ctx):
+        self.mixer.prepare(ctx)
+
+    def forward(self, ctx, x, pending, run):
+        import torch
+        ops = ctx.ops
+        ctx.after_norm = None
+        ready = ctx.memo.pop("prenormed", None)
+        if pending is None and ready is not None and ready[0] is self.pre1 and ready[1] == x.data_ptr():
+            h = ready[2]                    # the block before made this norm while it added its last output
+        else:
+            h = self.pre1.forward(ctx, x, pending)
+        nxt = ctx.next_first_norm
+        if not (nxt is not None and type(nxt) is type(self.pre1) and nxt.width == self.width):
+            nxt = None
+        steps = [(self.mixer, self.post1, self.post_w[0], (run,))]
+        if self.ffn is not None:
+            steps.append((self.ffn, self.post2, self.post_w[1], ()))
+        xa = None
+        for i, (part, post, w, args) in enumerate(steps):
+            y, bias = part.forward(ctx, h, *args)
+            if bias is not None:
+                raise ConfigError("a sandwich block cannot norm an output with a deferred bias")
+            last = i == len(steps) - 1
+            follow = (self.pre2 if not last else (nxt if self.side is None else None))
+            h = ctx.ws.get("normed", x.shape[0], (self.width,), ctx.dtype) if follow is not None else None
+            if last and self.side is not None and ctx.dtype != torch.float32:
+                xa = ctx.ws.get("stream_copy", x.shape[0], (self.width,), ctx.dtype)
+            ops.post_norm_add(x, y, w, post.eps, follow.weight if follow is not None else None,
+                              follow.eps if follow is not None else 0.0, h, xa)
+        if self.side is not None:
+            h = ctx.ws.get("normed", x.shape[0], (self.width,), ctx.dtype) if nxt is not None else None
+            self.side.forward(ctx, x, x if xa is None else xa, nxt, h)
+        if nxt is not None:
+            ctx.memo["prenormed"] = (nxt, x.data_ptr(), h)
+        return None
+
+
+register("block", "sandwich", SandwichBlock)

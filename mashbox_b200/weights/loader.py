@@ -23,7 +23,7 @@ from .safetensors_io import TensorSource
 @dataclass(frozen=True)
 class Want:
     name: str                    # canonical name
-    shape: tuple
+    shape: tuple                 # an extent of -1: whatever the stored tensor has
     role: str = "matrix"         # matrix | vector | table | keep
     optional: bool = False
 
@@ -63,7 +63,9 @@ def load_tensors(source: TensorSource, wants, canonical: Callable, compute_dtype
     wrong = []
     for name, (stored, _) in found.items():
         _, shape = source.info(stored)
-        if tuple(shape) != tuple(wanted[name].shape):
+        want = tuple(wanted[name].shape)
+        # a wanted extent of -1 is read from the stored tensor (an inner width that only the checkpoint knows)
+        if len(shape) != len(want) or any(w != -1 and int(s) != int(w) for s, w in zip(shape, want)):
             wrong.append(f"{stored} is {list(shape)}, the configuration says {list(wanted[name].shape)}")
     if missing or unexpected or wrong:
         parts = []
