@@ -38,8 +38,12 @@ class ModelRunner:
         self.dtype = torch_dtype(engine_config.dtype)
         self.env = Env(self.dtype, self.device, kernels)
         needs, states = model.cache_needs()
+        # a model whose parts bound a sequence's length (a learned position table) bounds the context of every request
+        limit = model.context_limit() if hasattr(model, "context_limit") else None
+        context = engine_config.max_context or engine_config.pages() * engine_config.page_size
         self.cache = CacheManager(needs, states, engine_config.page_size, engine_config.pages(),
-                                  engine_config.max_requests, engine_config.max_context, self.dtype, self.device)
+                                  engine_config.max_requests, min(context, limit) if limit else engine_config.max_context,
+                                  self.dtype, self.device)
         self.options.setdefault("logit_rows", engine_config.max_requests)
         self.ws = Workspace(self.device, engine_config.max_tokens_per_step + engine_config.max_requests)
         self.inputs = StepInputs(self.device)

@@ -49,6 +49,12 @@ class Model:
         import math
         return math.lcm(*[max(1, int(getattr(p, "portion_alignment", 1))) for p in self.parts()])
 
+    def context_limit(self):
+        """the most positions a sequence may have, from the parts that bound it (a learned position table has that
+        many rows); None: no part bounds it"""
+        limits = [int(p.context_limit) for p in self.parts() if getattr(p, "context_limit", None)]
+        return min(limits) if limits else None
+
     def cache_needs(self):
         """-> ({cache id: CacheNeed or None}, {state id: StateNeed}) from the schedule: the runs that touch a cache say
         what it holds (the same tensors; windows and blocks are merged so that every reader finds its keys)."""

@@ -30,6 +30,7 @@ class PositionedEmbedding(Embedding):
                  scale=1.0):
         super().__init__(vocab, hidden, name, scale)
         self.P, self.position_name = int(max_positions), position_name
+        self.context_limit = self.P         # the engine admits no request that would grow beyond the table
         self.positions = None
 
     def wants(self):

@@ -1,0 +1,442 @@
+"""-m gpu: the Sufopel decoder in the engine against the plain implementation (tests/plain/sufopel.py), in float32 and
+bfloat16: single kernels on inputs built so that a fault shows (a state carried across cuts and slots, one loud latent
+far back, at a page's border, one position after the query), whole prompts, prefill against token-by-token decoding,
+portions down to two tokens, batches of unequal requests against each alone, pages and state slots used again, long
+decoding, and greedy generation through the engine's own entry point and scheduler."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests import sufopel_helpers as S
+from tests.gpu_harness import DEV, i32
+from tests.plain import sufopel as plain
+
+pytestmark = pytest.mark.gpu
+DTYPES = ("float32", "bfloat16")
+TD = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+KERNEL_BAR = {"float32": 2e-5, "bfloat16": 2e-2}          # of the largest value
+
+
+def kernel_close(got, want, dtype, what, bar=None):
+    got, want = np.asarray(got.detach().float().cpu(), np.float64), np.asarray(want, np.float64)
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    err = np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)
+    assert np.isfinite(got).all() and err <= (bar or KERNEL_BAR[dtype]), \
+        f"{what}: {dtype} worst error {err:.3e} of the largest value"
+
+
+def rnd(g, *shape, dtype="float32", scale=1.0):
+    """random values that the storage dtype holds exactly, as float64"""
+    return (torch.randn(*shape, generator=g) * scale).to(TD[dtype]).double()
+
+
+# ------------------------------------------------------------------------------------------------ single kernels
+@pytest.mark.parametrize("H,G,dim,vdim", [(4, 2, 16, 24), (3, 1, 40, 20), (2, 2, 8, 72), (2, 1, 64, 32), (1, 1, 128, 40)])
+def test_delta_rule_carries_its_state_across_any_cut(H, G, dim, vdim):
+    """three sequences advance side by side in portions of their own sizes (1 and 2 tokens among them), in state slots
+    that are not in order; the state lies inside a wider tensor"""
+    from mashbox_b200 import ops
+    g = torch.Generator().manual_seed(dim)
+    T = 41
+    unit = lambda x: x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-6)
+    seqs = []
+    for _ in range(3):
+        q, k = unit(rnd(g, T, G, dim)) * dim ** -0.5, unit(rnd(g, T, G, dim))
+        v, beta = rnd(g, T, H, vdim), torch.sigmoid(rnd(g, T, H))
+        dec = torch.exp(-torch.exp(rnd(g, H, scale=0.5))[None, :, None] * torch.nn.functional.softplus(rnd(g, T, H, dim)))
+        want = torch.stack([plain.delta_rule(q[:, h // (H // G)], k[:, h // (H // G)], v[:, h], dec[:, h], beta[:, h])
+                            for h in range(H)], 1)
+        seqs.append((q, k, v, dec, beta, want))
+    pad, n = 40, H * dim * vdim
+    state = torch.zeros(5, pad + n + 8, device=DEV)
+    slots = [3, 0, 4]
+    cuts = [[1, 1, 2, 1, 9, 8, 3, 16], [2, 2, 1, 7, 29], [5, 17, 1, 2, 16]]
+    at, got = [0, 0, 0], [[], [], []]
+    for step in range(max(len(c) for c in cuts)):
+        live = [s for s in range(3) if step < len(cuts[s])]
+        lens = [cuts[s][step] for s in live]
+        cat = lambda j, w: torch.cat([seqs[s][j][at[s]:at[s] + n_] for s, n_ in zip(live, lens)]).reshape(sum(lens), w) \
+            .float().to(DEV).contiguous()
+        q, k, v, dec, beta = cat(0, G * dim), cat(1, G * dim), cat(2, H * vdim), cat(3, H * dim), cat(4, H)
+        o = torch.full((sum(lens), H * vdim), float("nan"), device=DEV)
+        q_start = np.concatenate([[0], np.cumsum(lens)[:-1]])
+        ops.delta_rule(q, k, v, dec, beta, o, state[:, pad:pad + n], (i32(q_start), i32(lens), i32([slots[s] for s in live])),
+                       H, G, dim, vdim)
+        at_o = 0
+        for s, n_ in zip(live, lens):
+            got[s].append(o[at_o:at_o + n_].cpu())
+            at_o += n_
+            at[s] += n_
+    assert at == [T, T, T]
+    for s in range(3):
+        kernel_close(torch.cat(got[s]).reshape(T, H, vdim), seqs[s][5], "float32", f"delta rule, sequence {s}", 1e-5)
+    assert float(state[:, :pad].abs().max()) == 0.0 and float(state[:, pad + n:].abs().max()) == 0.0
+    assert float(state[1].abs().max()) == 0.0 and float(state[2].abs().max()) == 0.0       # slots nobody has
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,G,dim,vdim", [(4, 2, 16, 24), (3, 1, 40, 20), (2, 2, 64, 128)])
+def test_delta_gates_and_gated_norm(dtype, H, G, dim, vdim):
+    from mashbox_b200 import ops
+    g = torch.Generator().manual_seed(H)
+    N, low_w = 7, H + 5
+    qkv, low, wide = rnd(g, N, 2 * G * dim + H * vdim, dtype=dtype), rnd(g, N, low_w, dtype=dtype), rnd(g, N, H * dim + H * vdim, dtype=dtype, scale=2.0)
+    A, dt = rnd(g, H, scale=0.5), rnd(g, H * dim)
+    dev = lambda t, d=dtype: t.to(DEV, TD[d]).contiguous()
+    f = lambda *s: torch.empty(*s, device=DEV)
+    q, k, v, dec, beta = f(N, G * dim), f(N, G * dim), f(N, H * vdim), f(N, H * dim), f(N, H)
+    ops.delta_gates(dev(qkv), dev(low), dev(wide), dev(A, "float32"), dev(dt, "float32"), q, k, v, dec, beta, H, G, dim, vdim)
+    unit = lambda x: x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-6)
+    a = plain.silu(qkv)
+    kernel_close(q, (unit(a[:, :G * dim].view(N, G, dim)) * dim ** -0.5).reshape(N, -1), "float32", "unit queries")
+    kernel_close(k, unit(a[:, G * dim:2 * G * dim].view(N, G, dim)).reshape(N, -1), "float32", "unit keys")
+    kernel_close(v, a[:, 2 * G * dim:], "float32", "values")
+    kernel_close(beta, torch.sigmoid(low[:, :H]), "float32", "beta")
+    want = torch.exp(-torch.exp(A)[None, :, None] * torch.nn.functional.softplus(wide[:, :H * dim].view(N, H, dim) + dt.view(H, dim)))
+    kernel_close(dec, want.reshape(N, -1), "float32", "decays")
+    o, w = rnd(g, N, H * vdim), rnd(g, vdim)
+    out = torch.empty(N, H * vdim, device=DEV, dtype=TD[dtype])
+    ops.gated_rms(dev(o, "float32"), dev(wide)[:, H * dim:], dev(w, "float32"), out, H, vdim, 1e-5)
+    want = plain.rms(o.view(N, H, vdim), 1e-5, w) * torch.sigmoid(wide[:, H * dim:].view(N, H, vdim))
+    kernel_close(out, want.reshape(N, -1), dtype, "gated norm of the heads")
+
+
+@pytest.mark.parametrize("E,top,groups,keep", [(12, 3, 3, 2), (8, 2, 1, 1), (6, 1, 6, 2), (16, 2, 2, 1), (64, 6, 8, 3)])
+def test_expert_choice(E, top, groups, keep):
+    from mashbox_b200 import ops
+    g = torch.Generator().manual_seed(E)
+    N = 50
+    z = rnd(g, N, E, scale=1.5)
+    # three settings of the correction: none to speak of, one that reorders, one that makes every choice score negative
+    for corr in (torch.zeros(E, dtype=torch.float64), rnd(g, E, scale=0.5), rnd(g, E, scale=0.3) - 3.0):
+        W = {"l.mlp.router": torch.eye(E, dtype=torch.float64), "l.mlp.correction": corr}
+        chosen, weight = plain.route(W, "l.", dict(experts=E, top=top, groups=dict(count=groups, keep=keep)), z)
+        ids = torch.empty(N, top, dtype=torch.int32, device=DEV)
+        wts = torch.empty(N, top, device=DEV)
+        ops.moe_select(z.float().to(DEV), corr.float().to(DEV), ids, wts, groups, keep)
+        ids, wts = ids.cpu().long(), wts.cpu().double()
+        assert torch.equal(ids.sort(-1).values, chosen.sort(-1).values)
+        assert torch.allclose(wts, torch.sigmoid(z).gather(1, ids), atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("D,F", [(64, 32), (96, 24), (40, 50)])
+def test_experts_and_their_sum(dtype, D, F):
+    from mashbox_b200 import ops
+    g = torch.Generator().manual_seed(F)
+    N, E, top, limit = 9, 5, 2, 0.8
+    h = rnd(g, N, D, dtype=dtype)
+    W = {}
+    for e in range(E):
+        W[f"l.mlp.e{e}.gate"], W[f"l.mlp.e{e}.up"] = rnd(g, F, D, dtype=dtype, scale=0.3), rnd(g, F, D, dtype=dtype, scale=0.3)
+        W[f"l.mlp.e{e}.down"] = rnd(g, D, F, dtype=dtype, scale=0.3)
+    ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(N)])
+    wts = torch.rand(N, top, generator=g).double()
+    want = torch.stack([sum(wts[n, j] * plain.expert(W, "l.", int(ids[n, j]), h[n:n + 1], limit)[0] for j in range(top))
+                        for n in range(N)])
+    stack = lambda which: torch.stack([W[f"l.mlp.e{e}.{which}"] for e in range(E)]).to(DEV, TD[dtype]).contiguous()
+    y = torch.empty(N, top, D, device=DEV)
+    ops.moe_experts(h.to(DEV, TD[dtype]), ids.int().to(DEV), stack("gate"), stack("up"), stack("down"), y, limit, 1.702)
+    out = torch.empty(N, D, device=DEV, dtype=TD[dtype])
+    ops.moe_combine(y, wts.float().to(DEV), out)
+    kernel_close(out, want, dtype, "experts")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_row_kernels(dtype):
+    """learned positions, the norm of a sublayer's output with the next norm, the token's own input, the per-head
+    products"""
+    from mashbox_b200 import ops
+    g = torch.Generator().manual_seed(5)
+    N, D, V, P = 11, 72, 30, 20
+    dev = lambda t, d=dtype: t.to(DEV, TD[d]).contiguous()
+    table, pos = rnd(g, V, D, dtype=dtype), rnd(g, P, D, dtype=dtype)
+    tok, at = torch.randint(0, V, (N,), generator=g), torch.randint(0, P, (N,), generator=g)
+    x = torch.empty(N, D, device=DEV)
+    err = ops.new_error_word(DEV)
+    ops.embed_positions(i32(tok), i32(at), dev(table), dev(pos), x, err, 0.5)
+    kernel_close(x, table[tok] * 0.5 + pos[at], "float32", "embedding with positions")
+    assert int(err.item()) == 0
+    ops.embed_positions(i32(tok), i32(at + P), dev(table), dev(pos), x, err, 0.5)          # beyond the table: reported
+    assert int(err.item()) == 5
+    err.zero_()
+    # x += rms(delta) w;  y = rms(x) w2;  copy of x
+    x0, delta, w, w2 = rnd(g, N, D), rnd(g, N, D, dtype=dtype, scale=3.0), rnd(g, D), rnd(g, D)
+    x = dev(x0, "float32")
+    normed, copy = torch.empty(N, D, device=DEV, dtype=TD[dtype]), torch.empty(N, D, device=DEV, dtype=TD[dtype])
+    ops.post_norm_add(x, dev(delta), dev(w, "float32"), 1e-5, dev(w2, "float32"), 1e-6, normed, copy)
+    want = x0 + plain.rms(delta, 1e-5, w)
+    kernel_close(x, want, "float32", "stream after the normed output")
+    kernel_close(normed, plain.rms(want, 1e-6, w2), dtype, "the next norm")
+    kernel_close(copy, want, dtype, "copy of the stream")
+    x = dev(x0, "float32")
+    ops.post_norm_add(x, dev(delta), dev(w, "float32"), 1e-5)
+    kernel_close(x, want, "float32", "stream after the normed output, alone")
+    # g = gelu_tanh(z) * table[token, off:off + W]
+    Wd, off = 12, 24
+    z, side = rnd(g, N, Wd, dtype=dtype, scale=2.0), rnd(g, V, 48, dtype=dtype)
+    out = torch.empty(N, Wd, device=DEV, dtype=TD[dtype])
+    ops.gated_gather(dev(z), i32(tok), dev(side), off, out, err)
+    kernel_close(out, plain.gelu_tanh(z) * side[tok][:, off:off + Wd], dtype, "gated token input")
+    # per-head products from both sides
+    for heads, I, J, many in ((3, 16, 40, 11), (4, 24, 8, 11), (2, 40, 24, 70)):
+        a = rnd(g, many, heads * I, dtype=dtype)
+        wt, wn = rnd(g, heads * I, J, dtype=dtype, scale=0.3), rnd(g, heads * J, I, dtype=dtype, scale=0.3)
+        out = torch.empty(many, heads * J, device=DEV, dtype=TD[dtype])
+        ops.head_product(dev(a), dev(wt), out, heads, transposed=True)
+        kernel_close(out, torch.einsum("nhi,hij->nhj", a.view(many, heads, I), wt.view(heads, I, J)).reshape(many, -1), dtype,
+                     "W_h^T x_h")
+        ops.head_product(dev(a), dev(wn), out, heads, transposed=False)
+        kernel_close(out, torch.einsum("nhi,hji->nhj", a.view(many, heads, I), wn.view(heads, J, I)).reshape(many, -1), dtype,
+                     "W_h x_h")
+    # two stretches of a product's rows, each normed; the second into the page of the token's position
+    page, pages, wa, wb = 4, 9, 24, 16
+    rows, na, nb = rnd(g, N, wa + wb + 8, dtype=dtype), rnd(g, wa), rnd(g, wb)
+    table_rows = torch.tensor([[5, 2, 7, -1], [0, 8, 3, 1]], dtype=torch.int32)
+    tok_row, positions = torch.randint(0, 2, (N,), generator=g), torch.randperm(12, generator=g)[:N]
+    positions = torch.where(tok_row == 0, positions % 12, positions)
+    pool = torch.zeros(pages, 1, page, wb, device=DEV, dtype=TD[dtype])
+    out_a = torch.empty(N, wa, device=DEV, dtype=TD[dtype])
+    ops.rms_segments(dev(rows), 0, dev(na, "float32"), out_a, wa, dev(nb, "float32"), pool, i32(positions), i32(tok_row),
+                     table_rows.to(DEV), page, pages, 1e-5, err)
+    kernel_close(out_a, plain.rms(rows[:, :wa], 1e-5, na), dtype, "normed query latent")
+    want_b = plain.rms(rows[:, wa:wa + wb], 1e-5, nb)
+    seen = {}
+    for n in range(N):
+        seen[(int(tok_row[n]), int(positions[n]))] = n                           # a later token of the same place wins
+    for (r, p), n in seen.items():
+        kernel_close(pool[int(table_rows[r, p // page]), 0, p % page], want_b[n], dtype, f"latent of row {r}, position {p}")
+    assert int(err.item()) == 0
+
+
+def latent_case(dtype, H, dim, vdim, rank, lengths, q_lens, page, loud, seed=0):
+    """Sequences of latents in shuffled pages, the step's queries at each sequence's end.  loud: (sequence, key
+    position, query position) -- that latent and that query are scaled so that the one score stands out wherever the
+    query may see the key.  -> what the absorbed path computed and the plain, unabsorbed answer"""
+    from mashbox_b200 import ops
+    from mashbox_b200.parts.attention import PagedAttention
+    from tests.gpu_harness import PagedSequences
+    g = torch.Generator().manual_seed(seed)
+    scale = 0.3
+    uk, uv = rnd(g, H * dim, rank, dtype=dtype, scale=rank ** -0.5), rnd(g, H * vdim, rank, dtype=dtype, scale=rank ** -0.5)
+    seqs = PagedSequences(lengths, q_lens, H, 1, rank, page, TD[dtype], seed=seed)
+    q = [rnd(g, n, H, dim, dtype=dtype) for n in lengths]
+    c = [rnd(g, n, rank, dtype=dtype) for n in lengths]
+    for s, kp, qp in loud:
+        c[s][kp] *= 6.0
+        k = (c[s][kp] @ uk.T).view(H, dim)
+        q[s][qp] = (k / k.norm(dim=-1, keepdim=True) * 4.0).to(TD[dtype]).double()      # points at the loud key
+    want = []
+    for s, (n, ql) in enumerate(zip(lengths, q_lens)):
+        k, v = (c[s] @ uk.T).view(n, H, dim), (c[s] @ uv.T).view(n, H, vdim)
+        sc = torch.einsum("thd,shd->hts", q[s], k) * scale
+        sc = sc.masked_fill(~torch.ones(n, n, dtype=torch.bool).tril(), -math.inf)
+        want.append(torch.einsum("hts,shd->thd", torch.softmax(sc, -1), v)[n - ql:].reshape(ql, H * vdim))
+    seqs.k = [x[:, None, :] for x in c]
+    seqs.v = seqs.k
+    seqs.q = [torch.zeros(n, H, rank) for n in lengths]
+    seqs.build()
+    N = seqs.N
+    qs = torch.cat([q[s][n - ql:] for s, (n, ql) in enumerate(zip(lengths, q_lens))]).reshape(N, H * dim).to(DEV, TD[dtype])
+    qa = torch.empty(N, H * rank, device=DEV, dtype=TD[dtype])
+    ops.head_product(qs.contiguous(), uk.to(DEV, TD[dtype]).contiguous(), qa, H, transposed=True)
+    oa = torch.empty(N, H * rank, device=DEV, dtype=TD[dtype])
+    err = ops.new_error_word(DEV)
+    ops.attention_simple(qa, H * rank, oa, seqs.positions, seqs.tok_row, seqs.table, seqs.kpool, seqs.kpool, H, 1, rank, page,
+                         seqs.num_pages, None, scale, err)
+    o = torch.empty(N, H * vdim, device=DEV, dtype=TD[dtype])
+    ops.head_product(oa, uv.to(DEV, TD[dtype]).contiguous(), o, H, transposed=False)
+    assert int(err.item()) == 0
+    return o, torch.cat(want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,dim,vdim,rank,page", [(3, 16, 24, 40, 8), (4, 32, 16, 64, 16)])
+def test_latents_far_away_at_page_borders_and_after_the_query(dtype, H, dim, vdim, rank, page):
+    """one loud latent far back among hundreds; at the last slot of a page and the first of the next; at the query's own
+    position; and one position AFTER the query, which the query must not see; in a prompt's portion and decoded alone"""
+    n = 700
+    for q_lens, loud in (([1, 1, 1], [(0, 3, n - 1), (1, page * 5 - 1, n - 1), (2, page * 5, n - 1)]),
+                         ([300, 40, 2], [(0, 2, n - 7), (0, n - 100, n - 100), (0, n - 49, n - 50), (1, n - 17, n - 17),
+                                         (1, page * 3, n - 3), (2, n - 1, n - 2), (2, 0, n - 1)])):
+        got, want = latent_case(dtype, H, dim, vdim, rank, [n, n, n], q_lens, page, loud, seed=rank)
+        kernel_close(got, want, dtype, f"latent attention, query stretches {q_lens}", 3e-2 if dtype == "bfloat16" else 2e-5)
+    # the case is a test of something: without the causal mask the answer differs
+    got, want = latent_case("float32", H, dim, vdim, rank, [60], [2], page, [(0, 59, 58)], seed=1)
+    kernel_close(got, want, "float32", "a key one position after the query")
+    assert float((want[0] - want[1]).abs().max()) > 0.1
+
+
+# ------------------------------------------------------------------------------------------------ the model in the engine
+def runner_for(tmp, name, dtype, max_tokens, options=None, max_requests=4):
+    from mashbox_b200.engine.replay import make_runner
+    folder = S.make_folder(tmp, name, "float32" if dtype == "float32" else "bfloat16")
+    return folder, make_runner(folder, dtype, max_tokens, page_size=S.CONFIGS[name][2], options=options,
+                               max_requests=max_requests)
+
+
+def replay(runner, steps):
+    from mashbox_b200.engine.replay import run_step
+    out = {}
+    for i, s in enumerate(steps):
+        r = run_step(runner, dict(s, step=i))
+        if r is not None:
+            out[i] = r.numpy()
+    return out
+
+
+def cut_steps(rid, tokens, cuts, end=True):
+    """the steps that feed `tokens` in portions of the given sizes, asking for every position's logits"""
+    steps, at = [], 0
+    for n in cuts:
+        steps.append(dict(entries=[dict(id=rid, tokens=tokens[at:at + n], want=list(range(n)))], end=[]))
+        at += n
+    assert at == len(tokens)
+    if end:
+        steps[-1]["end"] = [rid]
+    return steps
+
+
+CASES = [(n, d) for n in S.CONFIGS for d in DTYPES]
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole_prompts_and_first_tokens(tmp_path_factory, name, dtype):
+    folder, runner = runner_for(tmp_path_factory.mktemp("m"), name, dtype, 320)
+    for p in S.prompts_for(name, (1, 2, 3, 5, 21, 64, 65, 150, 300)):
+        got = replay(runner, cut_steps("a", p, [len(p)]))[0]
+        S.assert_close(got, S.plain_logits(folder, p), dtype, f"{name}: whole prompt of {len(p)}")
+    runner.cache.check()
+    assert runner.cache.free_pages() == [runner.cache.num_pages] * len(runner.cache.groups)
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_prefill_against_token_by_token(tmp_path_factory, name, dtype):
+    """every token alone from the first one, over many pages, against the whole prompt in one step and against the
+    plain implementation; a second request in the same state slot and pages right after starts from nothing"""
+    folder, runner = runner_for(tmp_path_factory.mktemp("m"), name, dtype, 192, max_requests=1)
+    p, p2 = S.prompts_for(name, (170, 30), seed=1)
+    whole = replay(runner, cut_steps("a", p, [len(p)]))[0]
+    out = replay(runner, cut_steps("b", p, [1] * len(p)))
+    single = np.concatenate([out[i] for i in range(len(p))])
+    S.assert_close(single, S.plain_logits(folder, p), dtype, f"{name}: 170 tokens one by one")
+    S.assert_close(single, whole, dtype, f"{name}: one by one against one step", S.BAR_SAME)
+    again = replay(runner, cut_steps("c", p2, [len(p2)]))[0]
+    S.assert_close(again, S.plain_logits(folder, p2), dtype, f"{name}: a request in a slot that was used before")
+    runner.cache.check()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_portions_of_every_size(tmp_path_factory, name, dtype):
+    folder, runner = runner_for(tmp_path_factory.mktemp("m"), name, dtype, 256)
+    (p,) = S.prompts_for(name, (230,), seed=2)
+    want = S.plain_logits(folder, p)
+    whole = replay(runner, cut_steps("w", p, [len(p)]))[0]
+    for cuts in ([2] * 115, [3, 37, 1, 2, 64, 17, 2, 2, 1, 50, 33, 5, 7, 6], [7, 8, 9, 1, 15, 16, 17, 157],
+                 [63, 1, 1, 63, 2, 62, 38], [128, 2, 100]):
+        out = replay(runner, cut_steps("a", p, cuts))
+        got = np.concatenate([out[i] for i in range(len(cuts))])
+        S.assert_close(got, want, dtype, f"{name}: portions {cuts[:6]}...")
+        S.assert_close(got, whole, dtype, f"{name}: portions {cuts[:6]}... against one step", S.BAR_SAME)
+    runner.cache.check()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_unequal_requests_side_by_side_with_pages_and_slots_used_again(tmp_path_factory, name, dtype):
+    """Two requests at most are live, portions of some beside single tokens of others; the pool holds less than all
+    requests together, and two state slots only, so pages and slots come back and are taken again.  Every request's
+    logits must be those it has alone."""
+    folder, runner = runner_for(tmp_path_factory.mktemp("m"), name, dtype, 224, max_requests=2)
+    prompts = dict(zip("abcdef", S.prompts_for(name, (90, 47, 3, 110, 66, 21), seed=3)))
+    plans = dict(a=[30, 1, 1, 2, 50, 1, 1, 1, 1, 1, 1], b=[1, 1, 20, 2, 23], c=[1, 2], d=[64, 1, 40, 2, 1, 1, 1],
+                 e=[2, 62, 1, 1], f=[21])
+    order = ["a", "b", "c", "d", "e", "f"]
+    at = {r: 0 for r in order}
+    turn = {r: 0 for r in order}
+    got = {r: [] for r in order}
+    waiting, live, step = list(order), [], 0
+    from mashbox_b200.engine.replay import run_step
+    while waiting or live:
+        while waiting and len(live) < 2:
+            live.append(waiting.pop(0))
+        entries, end = [], []
+        for r in live:
+            n = plans[r][turn[r]]
+            entries.append(dict(id=r, tokens=prompts[r][at[r]:at[r] + n], want=list(range(n))))
+            at[r] += n
+            turn[r] += 1
+            if turn[r] == len(plans[r]):
+                assert at[r] == len(prompts[r])
+                end.append(r)
+        out = run_step(runner, dict(step=step, entries=entries, end=end)).numpy()
+        o = 0
+        for e in entries:
+            got[e["id"]].append(out[o:o + len(e["tokens"])])
+            o += len(e["tokens"])
+        live = [r for r in live if r not in end]
+        runner.cache.check()
+        step += 1
+    for r in order:
+        S.assert_close(np.concatenate(got[r]), S.plain_logits(folder, prompts[r]), dtype, f"{name}: request {r} in a batch")
+    assert runner.cache.free_pages() == [runner.cache.num_pages] * len(runner.cache.groups)
+
+
+@pytest.mark.parametrize("name,dtype", [("T", "float32"), ("T", "bfloat16"), ("V", "bfloat16")])
+def test_long_decoding(tmp_path_factory, name, dtype):
+    """a short prompt and 380 tokens one by one (graphs replayed), two requests side by side"""
+    folder, runner = runner_for(tmp_path_factory.mktemp("m"), name, dtype, 896)
+    a, b = S.prompts_for(name, (412, 380), seed=4)
+    steps = [dict(entries=[dict(id="a", tokens=a[:12], want=[11])], end=[]),
+             dict(entries=[dict(id="a", tokens=a[12:44], want=[31]), dict(id="b", tokens=b[:3], want=[2])], end=[])]
+    for i in range(400 - 32):
+        e = [dict(id="a", tokens=[a[44 + i]], want=[0])]
+        if 3 + i < len(b):
+            e.append(dict(id="b", tokens=[b[3 + i]], want=[0]))
+        steps.append(dict(entries=e, end=[]))
+    out = replay(runner, steps)
+    wa, wb = S.plain_logits(folder, a), S.plain_logits(folder, b)
+    ga = np.stack([out[0][0], out[1][0]] + [out[2 + i][0] for i in range(368)])
+    gb = np.stack([out[1][1]] + [out[2 + i][1] for i in range(368)])
+    S.assert_close(ga, wa[[11, 43] + list(range(44, 412))], dtype, f"{name}: 368 tokens decoded, request a")
+    S.assert_close(gb, wb[[2] + list(range(3, 371))], dtype, f"{name}: 368 tokens decoded, request b")
+    assert runner.stats["graph_replays"] > 300
+    runner.cache.check()
+
+
+def test_a_request_beyond_the_position_table_is_refused(tmp_path_factory):
+    from mashbox_b200.engine.engine import Engine
+    folder = S.make_folder(tmp_path_factory.mktemp("m"), "T")
+    eng = Engine.from_folder(folder, dtype="float32", page_size=8, max_tokens=1024, max_requests=2)
+    limit = S.SUF_T.max_positions
+    assert eng.cache.max_context == limit
+    (p,) = S.prompts_for("T", (limit - 3,), seed=6)
+    assert eng.check(dict(ids=p, max_new=8)) is not None and eng.check(dict(ids=p, max_new=3)) is None
+
+
+@pytest.mark.parametrize("name,dtype", [("T", "float32"), ("U", "float32"), ("V", "bfloat16")])
+def test_greedy_generation_through_the_engine(tmp_path_factory, name, dtype):
+    """Engine.generate with its scheduler, graphs and sampler: three prompts of unequal length in portions of at most
+    32 tokens; in float32 the ids are the plain implementation's greedy ids."""
+    from mashbox_b200.engine.engine import Engine
+    folder = S.make_folder(tmp_path_factory.mktemp("m"), name, "float32" if dtype == "float32" else "bfloat16")
+    eng = Engine.from_folder(folder, dtype=dtype, page_size=S.CONFIGS[name][2], max_tokens=512, max_requests=3, chunk=32,
+                             max_tokens_per_step=40)
+    prompts = S.prompts_for(name, (70, 5, 33), seed=5)
+    new = 40
+    r = eng.generate(prompts, max_new=new)
+    assert r["finish"] == ["length"] * 3 and all(len(ids) == new for ids in r["ids"])
+    again = eng.generate(prompts, max_new=new)                            # captured graphs now
+    assert again["ids"] == r["ids"]
+    assert eng.runner.stats["graph_replays"] > 0
+    for p, ids in zip(prompts, r["ids"]):
+        lg = S.plain_logits(folder, p + ids)
+        for t, tok in enumerate(ids):
+            row = lg[len(p) + t - 1]
+            best = int(row.argmax())
+            if dtype == "float32":
+                assert tok == best or row[best] - row[tok] < 1e-4, f"{name}: token {t} is {tok}, plain says {best}"
+            else:                                                          # bf16 may pick another of two near-equal ids
+                assert row[best] - row[tok] < 0.05 * (row.max() - row.min()), f"{name}: token {t} = {tok} is far from the best"
+    eng.cache.check()
