@@ -213,3 +213,198 @@ MB_API int mb_moe_combine_f32(const float* y, const float* wts, void* out, int N
 MB_API int mb_moe_combine_bf16(const float* y, const float* wts, void* out, int N, int D, int top, cudaStream_t st) {
     return moe_combine_launch<bf16>(y, wts, (bf16*)out, N, D, top, st);
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Steps of many tokens (bf16): the (token, place) pairs are sorted by expert on the device, and every expert's rows run
+// through tensor-core tiles, so an expert's matrices are read once per 64 of its rows instead of once per row.
+//
+//   moe_sort        one block: counts per expert, offsets, the pairs in expert order (`sorted`), and the list of tiles
+//                   (expert, first sorted row, rows <= 64); the launch sizes below depend on the number of pairs only,
+//                   blocks beyond the tiles that exist leave at once
+//   moe_grouped<0>  rows gathered from h by token, [Wg_e; Wu_e]: act = g sigmoid(alpha g) (u + 1) with the clamps, bf16,
+//                   at the pair's sorted row
+//   moe_grouped<1>  rows of act, Wd_e: float32 to the pair's own place in y (N, top, D), which moe_combine sums
+//
+// A tile is 64 rows x 64 output columns (of both matrices in mode 0), k in steps of 32 through two cp.async stages,
+// four warps of 16 rows each, ldmatrix + mma.sync.m16n8k16 with float accumulation.  A row's result does not depend on
+// where in its expert's run the sort put it.
+#define GG_TM 64
+#define GG_TN 64
+#define GG_TK 32
+#define GG_LD 40            // shared-memory row length in bf16: 80 bytes, so that 8 rows hit 8 different 16-byte columns
+
+__global__ void moe_sort_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ offsets, int* __restrict__ sorted,
+                                int* __restrict__ tiles /* 3 ints each */, int* __restrict__ n_tiles, int max_tiles) {
+    extern __shared__ int sh[];
+    int* cnt = sh;              // E
+    int* start = sh + E;        // E + 1
+    int* tstart = start + E + 1;  // E + 1
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        int e = ids[p];
+        if (e < 0 || e >= E) e = 0;
+        atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int a = 0, t = 0;
+        for (int e = 0; e < E; e++) {
+            start[e] = a; tstart[e] = t;
+            a += cnt[e];
+            t += (cnt[e] + GG_TM - 1) / GG_TM;
+        }
+        start[E] = a; tstart[E] = t;
+        *n_tiles = t < max_tiles ? t : max_tiles;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = start[e];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int nt = tstart[e + 1] - tstart[e];
+        for (int i = 0; i < nt; i++) {
+            const int t = tstart[e] + i;
+            if (t >= max_tiles) break;
+            tiles[3 * t] = e;
+            tiles[3 * t + 1] = start[e] + i * GG_TM;
+            tiles[3 * t + 2] = min(GG_TM, cnt[e] - i * GG_TM);
+        }
+        cnt[e] = start[e];                          // from here on: the next free sorted row of the expert
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        int e = ids[p];
+        if (e < 0 || e >= E) e = 0;
+        sorted[atomicAdd(&cnt[e], 1)] = p;
+    }
+}
+
+__device__ __forceinline__ void gg_cp16(void* smem, const void* gmem, bool valid) {
+    const uint32_t s = smem_u32(smem);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+
+__device__ __forceinline__ void gg_ldsm4(uint32_t (&r)[4], const void* p) {
+    const uint32_t s = smem_u32(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+
+__device__ __forceinline__ void gg_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// MODE 0: A = h (rows by token = pair / top), B0 = wg, B1 = wu (E, Nout, K), out_act (pairs, Nout) bf16 by sorted row.
+// MODE 1: A = act (rows by sorted row), B0 = wd (E, Nout, K), out_y (pairs, Nout) float32 by pair.
+template <int MODE>
+__global__ void __launch_bounds__(128)
+moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, const bf16* __restrict__ B1,
+                   const int* __restrict__ sorted, const int* __restrict__ tiles, const int* __restrict__ n_tiles, int top,
+                   int Nout, int K, bf16* __restrict__ out_act, float* __restrict__ out_y, float limit, float alpha) {
+    constexpr int NB = MODE == 0 ? 2 : 1;
+    __shared__ __align__(16) bf16 sA[2][GG_TM][GG_LD];
+    __shared__ __align__(16) bf16 sB[2][NB][GG_TN][GG_LD];
+    __shared__ int srow[GG_TM];                     // the pair of every row of the tile (-1: no row)
+    const int t = blockIdx.x;
+    if (t >= *n_tiles) return;
+    const int e = tiles[3 * t], r0 = tiles[3 * t + 1], rows = tiles[3 * t + 2];
+    const int n0 = blockIdx.y * GG_TN;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < GG_TM) srow[tid] = tid < rows ? sorted[r0 + tid] : -1;
+    __syncthreads();
+    const bf16* Bp[NB];
+    Bp[0] = B0 + (size_t)e * Nout * K;
+    if (MODE == 0) Bp[NB - 1] = B1 + (size_t)e * Nout * K;
+    // each thread copies chunks (row = c / 4, 8 k-values at (c % 4) * 8) c = tid and tid + 128 of every 64 x 32 tile
+    auto load = [&](int stage, int k0) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int c = tid + i * 128, r = c >> 2, kk = k0 + (c & 3) * 8;
+            const bool kin = kk < K;
+            const int pair = srow[r];
+            const size_t arow = MODE == 0 ? (size_t)(pair < 0 ? 0 : pair / top) : (size_t)(r0 + (r < rows ? r : 0));
+            gg_cp16(&sA[stage][r][(c & 3) * 8], A + arow * K + (kin ? kk : 0), kin && pair >= 0);
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                const int n = n0 + r;
+                gg_cp16(&sB[stage][b][r][(c & 3) * 8], Bp[b] + (size_t)(n < Nout ? n : 0) * K + (kin ? kk : 0), kin && n < Nout);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    float acc[NB][8][4];
+#pragma unroll
+    for (int b = 0; b < NB; b++)
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+#pragma unroll
+            for (int x = 0; x < 4; x++) acc[b][j][x] = 0.0f;
+    const int nk = (K + GG_TK - 1) / GG_TK;
+    load(0, 0);
+    for (int ks = 0; ks < nk; ks++) {
+        if (ks + 1 < nk) {
+            load((ks + 1) & 1, (ks + 1) * GG_TK);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
+        __syncthreads();
+        const int st = ks & 1;
+#pragma unroll
+        for (int k16 = 0; k16 < GG_TK; k16 += 16) {
+            uint32_t a[4];
+            gg_ldsm4(a, &sA[st][warp * 16 + (lane & 15)][k16 + (lane >> 4) * 8]);
+#pragma unroll
+            for (int b = 0; b < NB; b++)
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    uint32_t w[4];          // two n-tiles of 8: (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15)
+                    gg_ldsm4(w, &sB[st][b][j * 8 + (lane & 7) + (lane >> 4) * 8][k16 + ((lane >> 3) & 1) * 8]);
+                    gg_mma(acc[b][j], a, w[0], w[1]);
+                    gg_mma(acc[b][j + 1], a, w[2], w[3]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const int r = warp * 16 + (lane >> 2) + half * 8;
+        const int pair = srow[r];
+        if (pair < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+#pragma unroll
+            for (int x = 0; x < 2; x++) {
+                const int n = n0 + j * 8 + (lane & 3) * 2 + x;
+                if (n >= Nout) continue;
+                if (MODE == 0) {
+                    const float g = fminf(acc[0][j][half * 2 + x], limit);
+                    const float u = fminf(fmaxf(acc[NB - 1][j][half * 2 + x], -limit), limit);
+                    out_act[(size_t)(r0 + r) * Nout + n] = __float2bfloat16_rn(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+                } else {
+                    out_y[(size_t)pair * Nout + n] = acc[0][j][half * 2 + x];
+                }
+            }
+    }
+}
+
+// ids (N, top); sorted, offsets, tiles, n_tiles: int scratch of P, E + 1, 3 max_tiles and 1 values; act (P, F) bf16
+MB_API int mb_moe_grouped_bf16(const void* h, const int* ids, const void* wg, const void* wu, const void* wd, float* y,
+                               void* act, int* sorted, int* offsets, int* tiles, int* n_tiles, int N, int D, int F, int E,
+                               int top, float limit, float alpha, cudaStream_t st) {
+    if (N == 0) return 0;
+    const long long P = (long long)N * top;
+    if (D % 8 || F % 8 || D < 8 || F < 8 || E < 1 || E > 4096 || P > (1 << 24)) return -2;
+    const int max_tiles = (int)(P / GG_TM) + E;
+    moe_sort_kernel<<<1, 1024, (size_t)(3 * E + 2) * sizeof(int), st>>>(ids, (int)P, E, offsets, sorted, tiles, n_tiles, max_tiles);
+    MB_LAUNCH_CHECK();
+    moe_grouped_kernel<0><<<dim3(max_tiles, (F + GG_TN - 1) / GG_TN), 128, 0, st>>>(
+        (const bf16*)h, (const bf16*)wg, (const bf16*)wu, sorted, tiles, n_tiles, top, F, D, (bf16*)act, nullptr, limit, alpha);
+    MB_LAUNCH_CHECK();
+    moe_grouped_kernel<1><<<dim3(max_tiles, (D + GG_TN - 1) / GG_TN), 128, 0, st>>>(
+        (const bf16*)act, (const bf16*)wd, nullptr, sorted, tiles, n_tiles, top, D, F, nullptr, y, limit, alpha);
+    MB_LAUNCH_CHECK();
+    return 0;
+}

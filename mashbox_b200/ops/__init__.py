@@ -418,6 +418,41 @@ def moe_experts(h, ids, wg, wu, wd, y, limit, alpha):
              _stream()), "moe_experts")
 
 
+# Steps of more tokens than this run the experts on tensor-core tiles over the pairs sorted by expert (bf16 only).
+MOE_GROUPED = {"tokens": 16}
+
+
+def moe_grouped_supports(N, D, F, dtype):
+    return dtype == torch.bfloat16 and N > MOE_GROUPED["tokens"] and D % 8 == 0 and F % 8 == 0
+
+
+def moe_grouped_scratch(N, top, E):
+    """-> the number of int32 values moe_grouped needs as scratch"""
+    P = N * top
+    return P + (E + 1) + 3 * (P // 64 + E) + 1 + 3
+
+
+def moe_grouped(h, ids, wg, wu, wd, y, act, scratch, limit, alpha):
+    """moe_experts for steps of many tokens, bf16: the (token, place) pairs are sorted by expert on the device and every
+    expert's rows run through tensor-core tiles.  act (N * top, F) bf16 and scratch (moe_grouped_scratch values, int32)
+    are working memory."""
+    _cuda(h, ids, wg, wu, wd, y, act, scratch)
+    N, D = h.shape
+    E, F, _ = wg.shape
+    top = ids.shape[1]
+    P = N * top
+    max_tiles = P // 64 + E
+    if scratch.numel() < moe_grouped_scratch(N, top, E) or scratch.dtype != torch.int32:
+        raise KernelError("moe_grouped: the scratch is too small")
+    sorted_, offsets = scratch[:P], scratch[P:P + E + 1]
+    tiles = scratch[P + E + 1:P + E + 1 + 3 * max_tiles]
+    n_tiles = scratch[P + E + 1 + 3 * max_tiles:]
+    f = _fn("moe", "mb_moe_grouped_bf16", [c_void_p] * 11 + [c_int] * 5 + [c_float, c_float, c_void_p])
+    _check(f(_p(h), _p(ids), _p(wg), _p(wu), _p(wd), _p(y), _p(act), _p(sorted_), _p(offsets), _p(tiles), _p(n_tiles), N, D,
+             F, E, top, float(limit), float(alpha), _stream()), "moe_grouped")
+    COUNTERS["launches"] += 2
+
+
 def moe_combine(y, wts, out):
     """out[n] = sum_k wts[n, k] y[n, k] (places in order); y (N, top, D) float32, out (N, D) the activation dtype"""
     _cuda(y, wts, out)

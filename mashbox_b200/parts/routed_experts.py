@@ -7,8 +7,11 @@
 
 The correction moves the choice only: the weights are the plain scores, not renormalised.  The stored matrices of the
 experts (`e0`, `e1`, ...) are stacked at load into (experts, rows, columns) tensors.  A step: the router's product with
-a float32 result, one kernel that chooses (a warp per token), one kernel that runs every (token, chosen expert) pair --
-a block streams that expert's three matrices -- and one that sums a token's places in order.  The choice is made on
+a float32 result, one kernel that chooses (a warp per token), the experts, and one kernel that sums a token's places in
+order.  The experts of a step of few tokens (and of every float32 step) are one kernel with a block per (token, chosen
+expert) pair that streams that expert's three matrices; a bfloat16 step of more tokens sorts the pairs by expert on
+the device and runs every expert's rows through tensor-core tiles (gate and up with the activation in the epilogue,
+then down), so an expert's matrices are read once per 64 of its rows.  The choice is made on
 the device and every launch has a shape that follows from the number of tokens, so steps can be captured in graphs.
 """
 from ..errors import ConfigError
@@ -62,7 +65,13 @@ class RoutedExperts:
         wts = ctx.ws.get("router_weights", N, (self.top,), torch.float32)
         ops.moe_select(z, self.corr, ids, wts, self.groups, self.keep)
         y = ctx.ws.get("expert_out", N, (self.top, self.D), torch.float32)
-        ops.moe_experts(h, ids, self.wg, self.wu, self.wd, y, self.limit, self.alpha)
+        if ops.moe_grouped_supports(N, self.D, self.F, ctx.dtype) and not ctx.options.get("plain_experts", False):
+            act = ctx.ws.get("expert_act", N * self.top, (self.F,), ctx.dtype, reserve=ctx.ws.max_rows * self.top)
+            n = ops.moe_grouped_scratch(ctx.ws.max_rows, self.top, self.E)
+            scratch = ctx.ws.get("expert_sort", max(n, ops.moe_grouped_scratch(N, self.top, self.E)), (), torch.int32, reserve=n)
+            ops.moe_grouped(h, ids, self.wg, self.wu, self.wd, y, act, scratch, self.limit, self.alpha)
+        else:
+            ops.moe_experts(h, ids, self.wg, self.wu, self.wd, y, self.limit, self.alpha)
         delta = ctx.ws.get(out, N, (self.D,), ctx.dtype)
         ops.moe_combine(y, wts, delta)
         return delta, None

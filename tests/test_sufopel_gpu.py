@@ -144,6 +144,31 @@ def test_experts_and_their_sum(dtype, D, F):
     kernel_close(out, want, dtype, "experts")
 
 
+@pytest.mark.parametrize("D,F,N,E,top", [(64, 32, 150, 5, 2), (96, 24, 333, 7, 3), (40, 56, 65, 3, 1), (128, 200, 70, 9, 4)])
+def test_experts_on_tensor_core_tiles(D, F, N, E, top):
+    """the pairs sorted by expert, experts with many rows, with a few and with none; sizes that leave ragged tiles"""
+    from mashbox_b200 import ops
+    g = torch.Generator().manual_seed(D)
+    limit, bf = 0.9, torch.bfloat16
+    h = rnd(g, N, D, dtype="bfloat16")
+    wg, wu, wd = (rnd(g, E, a, b, dtype="bfloat16", scale=0.3) for a, b in ((F, D), (F, D), (D, F)))
+    ids = torch.stack([torch.randperm(E - 1, generator=g)[:top] for _ in range(N)])         # the last expert gets nobody
+    ids[:3, 0] = E - 1 if N == 65 else ids[:3, 0]                                            # ... or three rows
+    y = torch.full((N, top, D), float("nan"), device=DEV)
+    act = torch.empty(N * top, F, device=DEV, dtype=bf)
+    scratch = torch.empty(ops.moe_grouped_scratch(N, top, E), dtype=torch.int32, device=DEV)
+    ops.moe_grouped(h.to(DEV, bf), ids.int().to(DEV), wg.to(DEV, bf), wu.to(DEV, bf), wd.to(DEV, bf), y, act, scratch, limit, 1.702)
+    hh = h[:, None, :].expand(N, top, D)
+    gg = torch.clamp(torch.einsum("nkd,nkfd->nkf", hh, wg[ids]), max=limit)
+    uu = torch.clamp(torch.einsum("nkd,nkfd->nkf", hh, wu[ids]), -limit, limit)
+    a = (gg * torch.sigmoid(1.702 * gg) * (uu + 1.0)).to(bf).double()
+    want = torch.einsum("nkf,nkdf->nkd", a, wd[ids])
+    kernel_close(y, want, "bfloat16", "experts on tiles", 5e-3)
+    y2 = torch.empty(N, top, D, device=DEV)
+    ops.moe_experts(h.to(DEV, bf), ids.int().to(DEV), wg.to(DEV, bf), wu.to(DEV, bf), wd.to(DEV, bf), y2, limit, 1.702)
+    kernel_close(y2, want, "bfloat16", "experts pair by pair", 5e-3)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_row_kernels(dtype):
     """learned positions, the norm of a sublayer's output with the next norm, the token's own input, the per-head
