@@ -664,6 +664,39 @@ def design_configs(size, layers, vocab=32000):
     return lz, ll
 
 
+# Layer sizes for `--design sufopel`: three delta-rule layers to one latent-attention layer (which ends each run of four),
+# routed experts in all but the first layer, a per-layer token input.  Heads of 128 x 128, latents of 128 values (the head
+# sizes the engine's TMA and tcgen05 attention kernels take; models of this kind keep 512), experts of F values of which
+# `top` of `experts` are chosen.  The Llama decoder beside it has the same width, layers and heads and as many
+# feed-forward weights as a token's chosen experts.
+SUFOPEL_SIZES = {
+    "1b": dict(width=2048, heads=16, dim=128, q_rank=768, kv_rank=128, ff=1408, experts=64, top=6, groups=8, keep=4, rank=128,
+               side=256),
+    "3b": dict(width=3072, heads=24, dim=128, q_rank=1024, kv_rank=128, ff=1536, experts=64, top=6, groups=8, keep=4, rank=128,
+               side=256),
+    "8b": dict(width=4096, heads=32, dim=128, q_rank=1536, kv_rank=128, ff=2048, experts=64, top=8, groups=8, keep=4, rank=128,
+               side=256),
+}
+
+
+def sufopel_configs(size, layers, vocab=32000, context=8192):
+    from mashbox_b200.config.llama import LlamaConfig
+    from mashbox_b200.config.sufopel import DeltaMixer, DenseFF, LatentMixer, RoutedFF, SufopelConfig, SufopelLayer
+    z = SUFOPEL_SIZES[size]
+    D, H, dim = z["width"], z["heads"], z["dim"]
+    dl = DeltaMixer(heads=H, kv_heads=H, dim=dim, vdim=dim, conv=4, a_rank=z["rank"], g_rank=z["rank"])
+    la = LatentMixer(heads=H, dim=dim, vdim=dim, q_rank=z["q_rank"], kv_rank=z["kv_rank"], scale=dim ** -0.5)
+    moe = RoutedFF(ff=z["ff"], limit=7.0, experts=z["experts"], top=z["top"], groups=z["groups"], keep=z["keep"])
+    sf = SufopelConfig("Sufopel", width=D, vocab=vocab, max_positions=context + 2048, embedding_scale=1.0, logit_scale=1.0,
+                       norm_eps=1e-6, side_dim=z["side"], layers=tuple(
+        SufopelLayer("latent_attention" if i % 4 == 3 else "channel_delta", la if i % 4 == 3 else dl,
+                     DenseFF(z["ff"] * z["top"]) if i == 0 else moe) for i in range(layers)))
+    ll = LlamaConfig(architecture="LlamaForCausalLM", num_layers=layers, hidden=D, num_heads=H, num_kv_heads=max(1, H // 4),
+                     head_dim=dim, intermediate=z["ff"] * z["top"], vocab=vocab, rms_eps=1e-6, rope_theta=10000.0,
+                     rope_scaling=None, tie_embeddings=False, attention_bias=False, max_position=131072)
+    return sf, ll
+
+
 def run_design(a):
     """`--design luzosun --size 1b|3b|8b`: prefill and decode throughput of the Luzosun decoder and of the Llama decoder
     of equal size through the step function (random bf16 weights, `--layers` layers, default 4), and the kernels that
@@ -677,10 +710,17 @@ def run_design(a):
     torch.cuda.set_device(0)
     dev = "cuda:0"
     layers = a.layers or 4
-    z = DESIGN_SIZES[a.size]
-    cfgs = dict(zip(("luzosun", "llama"), design_configs(a.size, layers)))
+    design = a.design
+    if design == "sufopel":
+        z = SUFOPEL_SIZES[a.size]
+        cfgs = dict(zip((design, "llama"), sufopel_configs(a.size, layers, context=a.context)))
+        single_kernels = sufopel_kernels
+    else:
+        z = DESIGN_SIZES[a.size]
+        cfgs = dict(zip((design, "llama"), design_configs(a.size, layers)))
+        single_kernels = design_kernels
     K, W, B = a.steps, max(3, a.warmup), a.batch
-    ctx = min(a.context, z["block"])            # a Luzosun query reads its block of positions: both read `ctx` keys
+    ctx = min(a.context, z.get("block", a.context))    # a Luzosun query reads its block of positions: both read `ctx` keys
     P = a.prefill_tokens
     pk = peaks()
     ev = lambda: torch.cuda.Event(enable_timing=True)
@@ -689,8 +729,8 @@ def run_design(a):
     clocks.start()
     out = {}
     if a.kernels:                               # the single kernels only (also the workload of their ncu captures)
-        print(json.dumps({"impl": "ours", "design": "luzosun", "size": a.size, "prefill_tokens": P, "batch": B, "context": ctx,
-                          "peaks": pk, "kernels": design_kernels(a, z, P, B, ctx, pk), "clocks": clocks.stop()}))
+        print(json.dumps({"impl": "ours", "design": design, "size": a.size, "prefill_tokens": P, "batch": B, "context": ctx,
+                          "peaks": pk, "kernels": single_kernels(a, z, P, B, ctx, pk), "clocks": clocks.stop()}))
         return 0
     for name, cfg in cfgs.items():
         rand_ids = lambda n: torch.randint(0, cfg.vocab, (n,), generator=gen).tolist()
@@ -742,11 +782,135 @@ def run_design(a):
             cache.release(r)
         del eng, runner, cache
         torch.cuda.empty_cache()
-    out["kernels"] = design_kernels(a, z, P, B, ctx, pk)
-    out["ratio_luzosun_to_llama"] = {k: out["luzosun"][k] / out["llama"][k] for k in ("prefill_tokens_per_s", "decode_tokens_per_s")}
-    print(json.dumps({"impl": "ours", "design": "luzosun", "size": a.size, "layers": layers, "prefill_tokens": P, "batch": B,
+    out["kernels"] = single_kernels(a, z, P, B, ctx, pk)
+    out[f"ratio_{design}_to_llama"] = {k: out[design][k] / out["llama"][k] for k in ("prefill_tokens_per_s", "decode_tokens_per_s")}
+    print(json.dumps({"impl": "ours", "design": design, "size": a.size, "layers": layers, "prefill_tokens": P, "batch": B,
                       "context": ctx, "dtype": "bf16", "data": "synthetic", "peaks": pk, "clocks": clocks.stop(), **out}))
     return 0
+
+
+def sufopel_kernels(a, z, P, B, ctx, pk):
+    """The kernels of the Sufopel decoder, each beside the Llama decoder's kernel of the like job at equal sizes: CUDA-event
+    time of single launches after an L2 flush, and the fraction of the measured peak (copy bandwidth for the memory-bound
+    ones, bf16 tensor throughput for the products) that the algorithmic bytes or FLOPs come to."""
+    import torch
+    from mashbox_b200 import ops
+    from mashbox_b200.parts.attention import PagedAttention
+    dev = "cuda:0"
+    D, H, dim, R, F, E, top, page = z["width"], z["heads"], z["dim"], z["kv_rank"], z["ff"], z["experts"], z["top"], 16
+    gen = torch.Generator(device=dev).manual_seed(0)
+    bf = lambda *s: (torch.randn(*s, generator=gen, device=dev) * 0.5).to(torch.bfloat16)
+    f32 = lambda *s: torch.randn(*s, generator=gen, device=dev) * 0.5
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    err = ops.new_error_word(dev)
+
+    def timed(f):
+        for _ in range(3):
+            f()
+        ts = []
+        for _ in range(max(5, a.steps // 4)):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(ts)
+
+    mem = lambda us, nbytes: {"us": us, "gbs": nbytes / us / 1e3, "frac_of_copy_peak": nbytes / us / 1e3 / pk["hbm_gbs"]}
+    mat = lambda us, flops: {"us": us, "tflops": flops / us / 1e6, "frac_of_bf16_peak": flops / us / 1e6 / pk["bf16_tflops"]}
+    res = {}
+    # ---- the recurrence: a prompt of P tokens; B sequences of one token (state in, state out)
+    for form, N, S in (("prompt", P, 1), ("decode", B, B)):
+        q, k = f32(N, H * dim), f32(N, H * dim)
+        v, g, beta, o = f32(N, H * dim), torch.rand(N, H * dim, generator=gen, device=dev), torch.rand(N, H, generator=gen, device=dev), f32(N, H * dim)
+        state = torch.zeros(S, H * dim * dim, device=dev)
+        seq = (i32([i * (N // S) for i in range(S)]), i32([N // S] * S), i32(list(range(S))))
+        us = timed(lambda: ops.delta_rule(q, k, v, g, beta, o, state, seq, H, H, dim, dim))
+        r = mem(us, 2 * S * H * dim * dim * 4 + N * H * dim * 5 * 4)
+        r["gflops_fp32"] = N * H * dim * dim * 7 / us / 1e3                 # decay, two dot products, update: 7 per element
+        res[f"delta_rule_{form}"] = r
+    # ---- Llama's attention at equal heads, beside it: P prompt tokens; B tokens over ctx keys
+    att = PagedAttention(H, max(1, H // 4), dim)
+    lat = PagedAttention(H, 1, R, None, dim ** -0.5)
+    for name, core, width in (("attention_llama", att, dim), ("latent_attention", lat, R)):
+        for form, N, S, klen in (("prompt", P, 1, P), ("decode", B, B, ctx)):
+            pages = S * -(-klen // page)
+            table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(S, -1)
+            kp, vp = bf(pages, core.KV, page, width), bf(pages, core.KV, page, width)
+            if core is lat:
+                vp = kp                                 # a position's latent is key and value at once
+            q, o = bf(N, H * width), torch.empty(N, H * width, device=dev, dtype=torch.bfloat16)
+            q_len = [N // S] * S
+            ctx_ = _PlanContext(ops, dev, q_len, [klen - n for n in q_len], page, pages, err)
+            core.prepare(ctx_)
+            ctx_.inputs.upload()
+            us = timed(lambda: core.attend(ctx_, q, H * width, o, table, kp, vp))
+            nbytes = (1 if core is lat else 2) * S * klen * core.KV * width * 2 + 2 * N * H * width * 2
+            if form == "prompt":
+                res[f"{name}_prompt"] = mat(us, 4 * H * width * P * P / 2)
+            else:
+                res[f"{name}_decode"] = mem(us, nbytes)
+    # ---- the experts: P tokens on tiles; B tokens pair by pair; Llama's feed-forward products of as many weights
+    wg, wu, wd = bf(E, F, D), bf(E, F, D), bf(E, D, F)
+    for form, N in (("prompt", P), ("decode", B)):
+        h = bf(N, D)
+        ids = torch.stack([torch.randperm(E, generator=gen, device=dev)[:top] for _ in range(N)]).int().contiguous()
+        y = torch.empty(N, top, D, device=dev)
+        if form == "prompt":
+            act = torch.empty(N * top, F, device=dev, dtype=torch.bfloat16)
+            scratch = torch.empty(ops.moe_grouped_scratch(N, top, E), dtype=torch.int32, device=dev)
+            us = timed(lambda: ops.moe_grouped(h, ids, wg, wu, wd, y, act, scratch, 7.0, 1.702))
+            res["experts_prompt"] = mat(us, 2 * N * top * 3 * F * D)
+            wgu, wdn, a1, o1 = bf(2 * F * top, D), bf(D, F * top), torch.empty(N, F * top, device=dev, dtype=torch.bfloat16), torch.empty(N, D, device=dev, dtype=torch.bfloat16)
+            us = timed(lambda: (ops.linear_swiglu(h, wgu, a1), ops.linear(a1, wdn, out=o1)))
+            res["feed_forward_llama_prompt"] = mat(us, 2 * N * top * 3 * F * D)
+        else:
+            us = timed(lambda: ops.moe_experts(h, ids, wg, wu, wd, y, 7.0, 1.702))
+            touched = len(set(ids.flatten().tolist()))
+            res["experts_decode"] = mem(us, touched * 3 * F * D * 2)
+            res["experts_decode"]["experts_touched"] = touched
+            wgu, wdn, a1, o1 = bf(2 * F * top, D), bf(D, F * top), torch.empty(N, F * top, device=dev, dtype=torch.bfloat16), torch.empty(N, D, device=dev, dtype=torch.bfloat16)
+            us = timed(lambda: (ops.linear_swiglu(h, wgu, a1) if ops.fused_swiglu_supports(N, F * top, D) else
+                                ops.linear_stream(h, wgu, a1, "swiglu"), ops.linear(a1, wdn, out=o1)))
+            res["feed_forward_llama_decode"] = mem(us, 3 * F * top * D * 2)
+    # ---- the norm around a sublayer's output, beside Llama's add + norm
+    for form, N in (("prompt", P), ("decode", B)):
+        x, delta, w, nrm = f32(N, D), bf(N, D), f32(D), torch.empty(N, D, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda: ops.post_norm_add(x, delta, w, 1e-6, w, 1e-6, nrm))
+        res[f"post_norm_add_{form}"] = mem(us, N * D * (4 + 4 + 2 + 2))
+        us = timed(lambda: ops.add_rmsnorm(x, delta, None, w, 1e-6, nrm))
+        res[f"add_norm_llama_{form}"] = mem(us, N * D * (4 + 4 + 2 + 2))
+    return res
+
+
+class _PlanContext:
+    """the part of a step's context that the attention plan and kernels read, for timing them outside a model"""
+
+    def __init__(self, ops, dev, q_len, pos0, page, pages, err):
+        import numpy as np
+        import torch
+        from mashbox_b200.parts import StepInputs, Workspace
+        S, N = len(q_len), sum(q_len)
+        self.ops, self.device, self.dtype, self.err, self.options, self.memo = ops, dev, torch.bfloat16, err, {}, {}
+        self.N, self.S, self.q_len, self.pos0 = N, S, list(q_len), list(pos0)
+        self.q_start = [int(v) for v in np.concatenate([[0], np.cumsum(q_len)[:-1]])]
+        self.rows = list(range(S))
+        self.ws = Workspace(dev, N)
+        self.inputs = StepInputs(dev)
+        self.inputs.add("positions", np.concatenate([p + np.arange(n) for p, n in zip(pos0, q_len)]))
+        self.inputs.add("tok_row", np.repeat(np.arange(S), q_len))
+        for name, v in (("q_start", self.q_start), ("q_len", q_len), ("pos0", pos0), ("seq_row", self.rows)):
+            self.inputs.add(name, v)
+
+        class _Cache:
+            page_size, pool_pages = page, pages
+        self.cache = _Cache()
+
+    def dev(self, name):
+        return self.inputs.get(name)
 
 
 def design_kernels(a, z, P, B, ctx, pk):
@@ -915,7 +1079,7 @@ def main():
     ap.add_argument("--requests", type=int, default=0, help="workloads: fewer requests than the workload names")
     ap.add_argument("--pool-tokens", type=int, default=0, help="workloads: size of the cache pool (0: every request fits)")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--design", default="", choices=("", "luzosun"),
+    ap.add_argument("--design", default="", choices=("", "luzosun", "sufopel"),
                     help="another design beside the Llama decoder of equal size (prefill, decode, single kernels)")
     ap.add_argument("--size", default="8b", choices=tuple(DESIGN_SIZES), help="--design: the layer sizes")
     ap.add_argument("--workload-warm", type=int, default=1, help="workloads: run the workload once untimed first")

@@ -4,9 +4,9 @@
 //     S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
 // Column c of S (the dim values that belong to value channel c) never meets another column: S^T k and S^T q are dot
 // products along a column, and the update adds k times the column's own u.  So a column is the unit of work: LANES
-// threads hold it in registers, dim / LANES values each (channels lane, lane + LANES, ...), the two dot products are
-// partial sums met by shuffles, and a block of 32 columns walks a sequence's tokens in order, reading the token's q, k,
-// g (shared by all columns), v and beta from shared memory, BATCH tokens per block barrier.  A prompt of any length, a
+// threads hold it in registers, dim / LANES values each, the two dot products are partial sums (four chains a thread,
+// added pairwise) met by shuffles, and a block of 16 columns walks a sequence's tokens in order, reading the token's q,
+// k, g (shared by all columns), v and beta from shared memory, BATCH tokens per block barrier.  A prompt of any length, a
 // portion and a single decoded token are the same loop; the state is read once and written once per step.  Every sum
 // runs in a fixed order, so the result does not depend on how a prompt was cut into steps.
 //
@@ -16,9 +16,14 @@
 //   gated_rms     o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) per head, to the storage type
 #include "common.cuh"
 
-#define DR_LANES 4
-#define DR_COLS 32
+#define DR_LANES 8
+#define DR_COLS 16
 #define DR_BATCH 8
+
+// 4 bytes from global to shared memory without a register in between; size 0: the destination is set to zero
+__device__ __forceinline__ void dr_cp4(float* smem, const float* gmem, int size) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(size));
+}
 
 __device__ __forceinline__ float dr_silu(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float dr_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
@@ -57,16 +62,19 @@ __global__ void delta_gates_kernel(const T* __restrict__ qkv, const T* __restric
     if (threadIdx.x == 0) beta[(size_t)n * H + h] = dr_sigmoid(mb_load(low + (size_t)n * low_stride + h));
 }
 
-// grid (column tiles, H, sequences), DR_COLS * DR_LANES threads.  R: state values per thread, dim <= R * DR_LANES.
+// grid (column tiles, H, sequences), DR_COLS * DR_LANES threads.  R: state values per thread (a multiple of 4),
+// dim <= R * DR_LANES = DP.  Thread (column, lane) holds channels r4 * 4 DR_LANES + lane * 4 + c (r4 < R / 4, c < 4), so
+// that its reads of a token's q, k, g are 16-byte loads and the lanes of a column read one contiguous stretch.  The
+// next DR_BATCH tokens are sent for (cp.async, zero fill beyond dim and vdim) while the current ones are worked on.
 template <int R>
 __global__ void __launch_bounds__(DR_COLS * DR_LANES)
 delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ g, const float* __restrict__ beta, float* __restrict__ o,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
                   const int* __restrict__ q_len, const int* __restrict__ state_slot, int H, int G, int dim, int vdim) {
-    constexpr int DP = R * DR_LANES;                       // padded dim
-    __shared__ float sq[DR_BATCH][DP], sk[DR_BATCH][DP], sg[DR_BATCH][DP];
-    __shared__ float sv[DR_BATCH][DR_COLS], sb[DR_BATCH];
+    constexpr int DP = R * DR_LANES, R4 = R / 4, BT = R >= 32 ? DR_BATCH / 2 : DR_BATCH;
+    __shared__ __align__(16) float sq[2][BT][DP], sk[2][BT][DP], sg[2][BT][DP];
+    __shared__ float sv[2][BT][DR_COLS], sb[2][BT];
     const int s = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * DR_COLS;
     const int lane = threadIdx.x & (DR_LANES - 1), cl = threadIdx.x / DR_LANES, col = col0 + cl;
     const bool live = col < vdim;
@@ -74,55 +82,79 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     float* S = state + (size_t)state_slot[s] * state_stride + (size_t)h * dim * vdim;
     float st[R];
 #pragma unroll
-    for (int r = 0; r < R; r++) {
-        const int i = lane + r * DR_LANES;
-        st[r] = (live && i < dim) ? S[(size_t)i * vdim + col] : 0.0f;
-    }
-    for (int t0 = 0; t0 < len; t0 += DR_BATCH) {
-        const int nb = min(DR_BATCH, len - t0);
-        __syncthreads();
+    for (int r4 = 0; r4 < R4; r4++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int i = r4 * 4 * DR_LANES + lane * 4 + c;
+            st[r4 * 4 + c] = (live && i < dim) ? S[(size_t)i * vdim + col] : 0.0f;
+        }
+    auto fetch = [&](int buf, int t0) {
+        const int nb = min(BT, len - t0);
         for (int idx = threadIdx.x; idx < nb * DP; idx += blockDim.x) {
             const int tt = idx / DP, i = idx - tt * DP;
             const size_t n = (size_t)(a + t0 + tt);
-            const bool in = i < dim;
-            sq[tt][i] = in ? q[(n * G + j) * dim + i] : 0.0f;
-            sk[tt][i] = in ? k[(n * G + j) * dim + i] : 0.0f;
-            sg[tt][i] = in ? g[(n * H + h) * dim + i] : 0.0f;
+            const int sz = i < dim ? 4 : 0;
+            const int ii = i < dim ? i : 0;
+            dr_cp4(&sq[buf][tt][i], q + (n * G + j) * dim + ii, sz);
+            dr_cp4(&sk[buf][tt][i], k + (n * G + j) * dim + ii, sz);
+            dr_cp4(&sg[buf][tt][i], g + (n * H + h) * dim + ii, sz);
         }
         for (int idx = threadIdx.x; idx < nb * DR_COLS; idx += blockDim.x) {
             const int tt = idx / DR_COLS, c = idx - tt * DR_COLS;
-            sv[tt][c] = (col0 + c < vdim) ? v[((size_t)(a + t0 + tt) * H + h) * vdim + col0 + c] : 0.0f;
+            const bool in = col0 + c < vdim;
+            dr_cp4(&sv[buf][tt][c], v + ((size_t)(a + t0 + tt) * H + h) * vdim + (in ? col0 + c : 0), in ? 4 : 0);
         }
-        if (threadIdx.x < nb) sb[threadIdx.x] = beta[(size_t)(a + t0 + threadIdx.x) * H + h];
+        if (threadIdx.x < nb) dr_cp4(&sb[buf][threadIdx.x], beta + (size_t)(a + t0 + threadIdx.x) * H + h, 4);
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    if (len > 0) fetch(0, 0);
+    for (int t0 = 0, it = 0; t0 < len; t0 += BT, it++) {
+        const int nb = min(BT, len - t0), buf = it & 1;
+        if (t0 + BT < len) {
+            fetch(buf ^ 1, t0 + BT);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
+        }
         __syncthreads();
         for (int tt = 0; tt < nb; tt++) {
-            float dot = 0.0f;
+            float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+            float4 kk[R4];
 #pragma unroll
-            for (int r = 0; r < R; r++) {
-                const int i = lane + r * DR_LANES;
-                st[r] *= sg[tt][i];
-                dot = fmaf(st[r], sk[tt][i], dot);
+            for (int r4 = 0; r4 < R4; r4++) {
+                const float4 gg = *reinterpret_cast<const float4*>(&sg[buf][tt][r4 * 4 * DR_LANES + lane * 4]);
+                kk[r4] = *reinterpret_cast<const float4*>(&sk[buf][tt][r4 * 4 * DR_LANES + lane * 4]);
+                st[r4 * 4 + 0] *= gg.x; st[r4 * 4 + 1] *= gg.y; st[r4 * 4 + 2] *= gg.z; st[r4 * 4 + 3] *= gg.w;
+                d0 = fmaf(st[r4 * 4 + 0], kk[r4].x, d0); d1 = fmaf(st[r4 * 4 + 1], kk[r4].y, d1);
+                d2 = fmaf(st[r4 * 4 + 2], kk[r4].z, d2); d3 = fmaf(st[r4 * 4 + 3], kk[r4].w, d3);
             }
+            float dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
             for (int m = 1; m < DR_LANES; m <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
-            const float u = sb[tt] * (sv[tt][cl] - dot);
-            float acc = 0.0f;
+            const float u = sb[buf][tt] * (sv[buf][tt][cl] - dot);
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-            for (int r = 0; r < R; r++) {
-                const int i = lane + r * DR_LANES;
-                st[r] = fmaf(sk[tt][i], u, st[r]);
-                acc = fmaf(st[r], sq[tt][i], acc);
+            for (int r4 = 0; r4 < R4; r4++) {
+                const float4 qq = *reinterpret_cast<const float4*>(&sq[buf][tt][r4 * 4 * DR_LANES + lane * 4]);
+                st[r4 * 4 + 0] = fmaf(kk[r4].x, u, st[r4 * 4 + 0]); st[r4 * 4 + 1] = fmaf(kk[r4].y, u, st[r4 * 4 + 1]);
+                st[r4 * 4 + 2] = fmaf(kk[r4].z, u, st[r4 * 4 + 2]); st[r4 * 4 + 3] = fmaf(kk[r4].w, u, st[r4 * 4 + 3]);
+                a0 = fmaf(st[r4 * 4 + 0], qq.x, a0); a1 = fmaf(st[r4 * 4 + 1], qq.y, a1);
+                a2 = fmaf(st[r4 * 4 + 2], qq.z, a2); a3 = fmaf(st[r4 * 4 + 3], qq.w, a3);
             }
+            float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
             for (int m = 1; m < DR_LANES; m <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
             if (lane == 0 && live) o[((size_t)(a + t0 + tt) * H + h) * vdim + col] = acc;
         }
+        __syncthreads();
     }
 #pragma unroll
-    for (int r = 0; r < R; r++) {
-        const int i = lane + r * DR_LANES;
-        if (live && i < dim) S[(size_t)i * vdim + col] = st[r];
-    }
+    for (int r4 = 0; r4 < R4; r4++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int i = r4 * 4 * DR_LANES + lane * 4 + c;
+            if (live && i < dim) S[(size_t)i * vdim + col] = st[r4 * 4 + c];
+        }
 }
 
 // grid (N, H): o (N, H vdim) float32 -> out in the storage type
@@ -172,7 +204,7 @@ MB_API int mb_delta_rule(const float* q, const float* k, const float* v, const f
                          float* state, long long state_stride, const int* q_start, const int* q_len, const int* state_slot,
                          int S, int H, int G, int dim, int vdim, cudaStream_t st) {
     if (S == 0) return 0;
-    if (G < 1 || H % G || H > 65535 || S > 65535 || dim < 1 || dim > 64 * DR_LANES || vdim < 1) return -2;
+    if (G < 1 || H % G || H > 65535 || S > 65535 || dim < 1 || dim > 32 * DR_LANES || vdim < 1) return -2;
     const dim3 grid((vdim + DR_COLS - 1) / DR_COLS, H, S), block(DR_COLS * DR_LANES);
 #define DR_CASE(R)                                                                                                         \
     if (dim <= R * DR_LANES) {                                                                                             \
@@ -181,7 +213,7 @@ MB_API int mb_delta_rule(const float* q, const float* k, const float* v, const f
         MB_LAUNCH_CHECK();                                                                                                 \
         return 0;                                                                                                          \
     }
-    DR_CASE(4) DR_CASE(8) DR_CASE(16) DR_CASE(24) DR_CASE(32) DR_CASE(48) DR_CASE(64)
+    DR_CASE(4) DR_CASE(8) DR_CASE(16) DR_CASE(32)
 #undef DR_CASE
     return -2;
 }

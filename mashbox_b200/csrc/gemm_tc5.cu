@@ -29,13 +29,21 @@
 #define G_STAGE_BYTES (G_A_BYTES + G_B_BYTES)
 
 // MODE 0: bf16 out (N, M); 1: SwiGLU, W has 2 * M rows, bf16 out (N, M); 2: float out (N, M); 3: bf16 out (N, M) =
-// xIELU of the product (ap z^2 + z / 2 for z > 0, an (e^z - 1 - z) + z / 2 otherwise)
+// xIELU of the product (ap z^2 + z / 2 for z > 0, an (e^z - 1 - z) + z / 2 otherwise); 4: as 1 with the gate of routed
+// experts, g = min(gate, ap), u = clamp(up, -ap, ap), out = g sigmoid(an g) (u + 1).
+//
+// Grouped form (tile_expert given): W is a stack of matrices of `expert_rows` rows each, and every tile of 128 rows of
+// act belongs to one of them -- tile_expert[token tile] says which, -1: the tile holds no rows and is passed over by
+// all three roles alike.  Rows of act are laid out so by whoever sorted them (an expert's rows start at a multiple of
+// 128).  A tile of features that reaches beyond M reads rows of the next matrix of the stack; those columns are not stored.
 template <int MODE>
 __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant__ CUtensorMap amap,
                                                            const __grid_constant__ CUtensorMap wmap,
                                                            void* __restrict__ out, int N, int M, int K, float ap,
-                                                           float an, int* err) {
-    constexpr int FEATS = MODE == 1 ? 128 : 256;          // output features of one tile
+                                                           float an, int* err, const int* __restrict__ tile_expert,
+                                                           int expert_rows) {
+    constexpr bool GATED = MODE == 1 || MODE == 4;
+    constexpr int FEATS = GATED ? 128 : 256;              // output features of one tile
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -68,6 +76,12 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
             int it = 0;                                               // stages issued so far
             for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
                 const int tok0 = (tile % tok_tiles) * G_BM, m0 = (tile / tok_tiles) * FEATS;
+                int wrow = 0;
+                if (tile_expert) {
+                    const int e = tile_expert[tile % tok_tiles];
+                    if (e < 0) continue;
+                    wrow = e * expert_rows;
+                }
                 bool ok = true;
                 for (int kb = 0; kb < kblocks && ok; kb++, it++) {
                     const int s = it % G_STAGES, round = it / G_STAGES;
@@ -75,8 +89,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
                     const uint32_t fb = full0 + 8 * s, a_dst = stage0 + s * G_STAGE_BYTES, b_dst = a_dst + G_A_BYTES;
                     mbar_expect_tx(fb, G_STAGE_BYTES);
                     tma_load_2d(a_dst, &amap, kb * G_BK, tok0, fb);
-                    tma_load_2d(b_dst, &wmap, kb * G_BK, m0, fb);
-                    tma_load_2d(b_dst + G_B_BYTES / 2, &wmap, kb * G_BK, MODE == 1 ? M + m0 : m0 + 128, fb);
+                    tma_load_2d(b_dst, &wmap, kb * G_BK, wrow + m0, fb);
+                    tma_load_2d(b_dst + G_B_BYTES / 2, &wmap, kb * G_BK, wrow + (GATED ? M + m0 : m0 + 128), fb);
                 }
                 if (!ok) break;
             }
@@ -85,8 +99,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(G_BM, G_BN);
             int it = 0, j = 0;                                        // stages consumed, tiles done by this block
-            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, j++) {
+            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+                if (tile_expert && tile_expert[tile % tok_tiles] < 0) continue;
                 const int acc = j & 1, use = j >> 1;
+                j++;
                 if (use > 0 && !mbar_wait(tempty0 + 8 * acc, (use - 1) & 1, err)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * G_BN;
@@ -109,8 +125,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
     } else {
         const int q = warp & 3;                                       // the 32 TMEM lanes this warp may read
         int j = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, j++) {
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+            if (tile_expert && tile_expert[tile % tok_tiles] < 0) continue;
             const int acc = j & 1, use = j >> 1;
+            j++;
             if (!mbar_wait(tfull0 + 8 * acc, use & 1, err)) break;
             tc_fence_after();
             const int tok = (tile % tok_tiles) * G_BM + q * 32 + lane, m0 = (tile / tok_tiles) * FEATS;
@@ -119,17 +137,23 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
             for (int c = 0; c < FEATS; c += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + c, r);
-                if (MODE == 1) {
+                if (GATED) {
                     uint32_t u[32];
                     tmem_ld32(taddr + 128 + c, u);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; i++) {
                         // gate and up pass through bf16 as they do when the products are separate kernels
-                        const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
-                        const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[i])));
-                        // fast exponential and division: no slow path for huge or tiny gate values
-                        r[i] = __float_as_uint(__fdividef(g, 1.0f + __expf(-g)) * up);
+                        float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
+                        float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[i])));
+                        if (MODE == 4) {
+                            g = fminf(g, ap);
+                            up = fminf(fmaxf(up, -ap), ap) + 1.0f;
+                            r[i] = __float_as_uint(__fdividef(g, 1.0f + __expf(-an * g)) * up);
+                        } else {
+                            // fast exponential and division: no slow path for huge or tiny gate values
+                            r[i] = __float_as_uint(__fdividef(g, 1.0f + __expf(-g)) * up);
+                        }
                     }
                 } else {
                     tmem_ld_wait();
@@ -182,7 +206,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
 
 template <int MODE>
 static int tc5_launch(const void* act, const void* W, void* out, int N, int M, int K, int* err, cudaStream_t st,
-                      float ap = 0.0f, float an = 0.0f) {
+                      float ap = 0.0f, float an = 0.0f, const int* tile_expert = nullptr, int experts = 1) {
     if (N == 0 || M == 0) return 0;
     if (K % 8 || M % 8 || K < 8 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(act) & 15) ||
         (reinterpret_cast<uintptr_t>(out) & 15))
@@ -190,7 +214,9 @@ static int tc5_launch(const void* act, const void* W, void* out, int N, int M, i
     CUtensorMap amap, wmap;
     int rc = matrix_map(act, N, K, 128, &amap);
     if (rc) return rc;
-    rc = matrix_map(W, (long long)(MODE == 1 ? 2 : 1) * M, K, 128, &wmap);
+    constexpr int PER = (MODE == 1 || MODE == 4) ? 2 : 1;
+    if (tile_expert && (experts < 1 || N % G_BM)) return -2;
+    rc = matrix_map(W, (long long)PER * M * experts, K, 128, &wmap);
     if (rc) return rc;
     const size_t smem = 1024 + (size_t)G_STAGES * G_STAGE_BYTES + (2 * G_STAGES + 4) * 8 + 16;
     static bool configured = false;
@@ -204,9 +230,10 @@ static int tc5_launch(const void* act, const void* W, void* out, int N, int M, i
         if (sms <= 0) sms = 148;
         configured = true;
     }
-    const int feats = MODE == 1 ? 128 : 256;
+    const int feats = PER == 2 ? 128 : 256;
     const int tiles = ((N + G_BM - 1) / G_BM) * ((M + feats - 1) / feats);
-    gemm_tc5_kernel<MODE><<<tiles < sms ? tiles : sms, 192, smem, st>>>(amap, wmap, out, N, M, K, ap, an, err);
+    gemm_tc5_kernel<MODE><<<tiles < sms ? tiles : sms, 192, smem, st>>>(amap, wmap, out, N, M, K, ap, an, err, tile_expert,
+                                                                        PER * M);
     MB_LAUNCH_CHECK();
     return 0;
 }
@@ -231,3 +258,19 @@ MB_API int mb_gemm_tc5_f32out(const void* act, const void* W, void* out, int N, 
     return tc5_launch<2>(act, W, out, N, M, K, err, st);
 }
 
+
+// Grouped forms: act (N, K) with N a multiple of 128, every 128 rows one expert's (tile_expert[N / 128]: its index, -1:
+// no rows); W a stack of `experts` matrices.  Gated: (experts, 2 M, K), gate rows then up rows of each expert,
+// out (N, M) bf16 = g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
+MB_API int mb_gemm_tc5_grouped_gated_bf16(const void* act, const void* W, void* out, int N, int M, int K,
+                                          const int* tile_expert, int experts, float limit, float alpha, int* err,
+                                          cudaStream_t st) {
+    if (!tile_expert) return -2;
+    return tc5_launch<4>(act, W, out, N, M, K, err, st, limit, alpha, tile_expert, experts);
+}
+// W (experts, M, K); out (N, M) float32
+MB_API int mb_gemm_tc5_grouped_f32out(const void* act, const void* W, void* out, int N, int M, int K, const int* tile_expert,
+                                      int experts, int* err, cudaStream_t st) {
+    if (!tile_expert) return -2;
+    return tc5_launch<2>(act, W, out, N, M, K, err, st, 0.0f, 0.0f, tile_expert, experts);
+}

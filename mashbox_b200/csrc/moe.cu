@@ -8,8 +8,9 @@
 //                  y = Wd (g sigmoid(alpha g) (u + 1)), left in float32 per (token, place)
 //   moe_combine    out[n] = sum over the places, in order, of weight * y
 //
-// moe_experts is the form for steps of few tokens: a block per (token, expert) streams that expert's three matrices once,
-// which is what a decode step has to read anyway.  Dot products run over lanes with 16-byte loads where rows allow.
+// moe_experts is the form for steps of few tokens (and of float32): blocks per (token, expert) stream that expert's
+// three matrices, which is what a decode step has to read anyway.  Dot products run over lanes with 16-byte loads where
+// rows allow.
 #include "common.cuh"
 #include <math.h>
 
@@ -114,37 +115,50 @@ __device__ __forceinline__ float lane_dot(const bf16* w, const float* x, int K, 
     return mb_warp_sum(acc);
 }
 
-// grid (N, top); dynamic shared: h[D], act[F].  wg, wu (E, F, D); wd (E, D, F); y (N, top, D) float32
+// Steps of few tokens, two kernels, each with a block per (pair, stretch of MOE_ROWS output rows) so that a step of a
+// handful of tokens still fills the device: gate and up with the activation, (pairs, F) float32; then down, into
+// y (N, top, D) float32.  Dynamic shared: the input row (D or F floats).  wg, wu (E, F, D); wd (E, D, F).
+#define MOE_ROWS 32
+
 template <typename T>
-__global__ void moe_experts_kernel(const T* __restrict__ h, const int* __restrict__ ids, const T* __restrict__ wg,
-                                   const T* __restrict__ wu, const T* __restrict__ wd, float* __restrict__ y, int D, int F,
-                                   int E, int top, float limit, float alpha) {
-    extern __shared__ float sm[];
-    float* hx = sm;
-    float* act = sm + D;
-    const int n = blockIdx.x, kk = blockIdx.y;
+__global__ void moe_experts_up_kernel(const T* __restrict__ h, const int* __restrict__ ids, const T* __restrict__ wg,
+                                      const T* __restrict__ wu, long long gu_stride, float* __restrict__ act, int D, int F,
+                                      int E, int top, float limit, float alpha) {
+    extern __shared__ float hx[];
+    const int pair = blockIdx.x, j0 = blockIdx.y * MOE_ROWS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-    int e = ids[(size_t)n * top + kk];
+    int e = ids[pair];
     if (e < 0 || e >= E) e = 0;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) hx[d] = mb_load(h + (size_t)n * D + d);
+    const T* row = h + (size_t)(pair / top) * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) hx[d] = mb_load(row + d);
     __syncthreads();
-    const T* g_rows = wg + (size_t)e * F * D;
-    const T* u_rows = wu + (size_t)e * F * D;
-    for (int j = warp; j < F; j += nwarp) {
+    const T* g_rows = wg + (size_t)e * gu_stride;            // an expert's gate and up rows may lie in one tensor
+    const T* u_rows = wu + (size_t)e * gu_stride;
+    for (int j = j0 + warp; j < min(F, j0 + MOE_ROWS); j += nwarp) {
         float g = lane_dot(g_rows + (size_t)j * D, hx, D, lane);
         float u = lane_dot(u_rows + (size_t)j * D, hx, D, lane);
         if (lane == 0) {
             g = fminf(g, limit);
             u = fminf(fmaxf(u, -limit), limit);
-            act[j] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+            act[(size_t)pair * F + j] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
         }
     }
+}
+
+template <typename T>
+__global__ void moe_experts_down_kernel(const float* __restrict__ act, const int* __restrict__ ids, const T* __restrict__ wd,
+                                        float* __restrict__ y, int D, int F, int E) {
+    extern __shared__ float ax[];
+    const int pair = blockIdx.x, d0 = blockIdx.y * MOE_ROWS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int e = ids[pair];
+    if (e < 0 || e >= E) e = 0;
+    for (int j = threadIdx.x; j < F; j += blockDim.x) ax[j] = act[(size_t)pair * F + j];
     __syncthreads();
     const T* d_rows = wd + (size_t)e * D * F;
-    float* out = y + ((size_t)n * top + kk) * D;
-    for (int d = warp; d < D; d += nwarp) {
-        const float v = lane_dot(d_rows + (size_t)d * F, act, F, lane);
-        if (lane == 0) out[d] = v;
+    for (int d = d0 + warp; d < min(D, d0 + MOE_ROWS); d += nwarp) {
+        const float v = lane_dot(d_rows + (size_t)d * F, ax, F, lane);
+        if (lane == 0) y[(size_t)pair * D + d] = v;
     }
 }
 
@@ -171,30 +185,34 @@ MB_API int mb_moe_select(const float* z, const float* correction, int* ids, floa
 }
 
 template <typename T>
-static int moe_experts_launch(const T* h, const int* ids, const T* wg, const T* wu, const T* wd, float* y, int N, int D, int F,
-                              int E, int top, float limit, float alpha, cudaStream_t st) {
+static int moe_experts_launch(const T* h, const int* ids, const T* wg, const T* wu, long long gu_stride, const T* wd, float* y,
+                              float* act, int N, int D, int F, int E, int top, float limit, float alpha, cudaStream_t st) {
     if (N == 0) return 0;
-    if (D < 1 || F < 1 || top < 1 || top > 65535 || (size_t)(D + F) * sizeof(float) > 96 * 1024) return -2;
-    const size_t smem = (size_t)(D + F) * sizeof(float);
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(moe_experts_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    moe_experts_kernel<T><<<dim3(N, top), 256, smem, st>>>(h, ids, wg, wu, wd, y, D, F, E, top, limit, alpha);
+    const long long P = (long long)N * top;
+    if (D < 1 || F < 1 || top < 1 || P > 0x7fffffff || D > 12000 || F > 12000 || (F + MOE_ROWS - 1) / MOE_ROWS > 65535 ||
+        (D + MOE_ROWS - 1) / MOE_ROWS > 65535)
+        return -2;
+    moe_experts_up_kernel<T><<<dim3((unsigned)P, (F + MOE_ROWS - 1) / MOE_ROWS), 256, (size_t)D * sizeof(float), st>>>(
+        h, ids, wg, wu, gu_stride, act, D, F, E, top, limit, alpha);
+    MB_LAUNCH_CHECK();
+    moe_experts_down_kernel<T><<<dim3((unsigned)P, (D + MOE_ROWS - 1) / MOE_ROWS), 256, (size_t)F * sizeof(float), st>>>(
+        act, ids, wd, y, D, F, E);
     MB_LAUNCH_CHECK();
     return 0;
 }
 
-MB_API int mb_moe_experts_f32(const void* h, const int* ids, const void* wg, const void* wu, const void* wd, float* y, int N,
-                              int D, int F, int E, int top, float limit, float alpha, cudaStream_t st) {
-    return moe_experts_launch<float>((const float*)h, ids, (const float*)wg, (const float*)wu, (const float*)wd, y, N, D, F, E,
-                                     top, limit, alpha, st);
+MB_API int mb_moe_experts_f32(const void* h, const int* ids, const void* wg, const void* wu, long long gu_stride,
+                              const void* wd, float* y, float* act, int N, int D, int F, int E, int top, float limit,
+                              float alpha, cudaStream_t st) {
+    return moe_experts_launch<float>((const float*)h, ids, (const float*)wg, (const float*)wu, gu_stride, (const float*)wd, y,
+                                     act, N, D, F, E, top, limit, alpha, st);
 }
 
-MB_API int mb_moe_experts_bf16(const void* h, const int* ids, const void* wg, const void* wu, const void* wd, float* y, int N,
-                               int D, int F, int E, int top, float limit, float alpha, cudaStream_t st) {
-    return moe_experts_launch<bf16>((const bf16*)h, ids, (const bf16*)wg, (const bf16*)wu, (const bf16*)wd, y, N, D, F, E, top,
-                                    limit, alpha, st);
+MB_API int mb_moe_experts_bf16(const void* h, const int* ids, const void* wg, const void* wu, long long gu_stride,
+                               const void* wd, float* y, float* act, int N, int D, int F, int E, int top, float limit,
+                               float alpha, cudaStream_t st) {
+    return moe_experts_launch<bf16>((const bf16*)h, ids, (const bf16*)wg, (const bf16*)wu, gu_stride, (const bf16*)wd, y, act,
+                                    N, D, F, E, top, limit, alpha, st);
 }
 
 template <typename T>
@@ -300,7 +318,7 @@ __device__ __forceinline__ void gg_mma(float (&c)[4], const uint32_t (&a)[4], ui
 // MODE 1: A = act (rows by sorted row), B0 = wd (E, Nout, K), out_y (pairs, Nout) float32 by pair.
 template <int MODE>
 __global__ void __launch_bounds__(128)
-moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, const bf16* __restrict__ B1,
+moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, const bf16* __restrict__ B1, long long b_stride,
                    const int* __restrict__ sorted, const int* __restrict__ tiles, const int* __restrict__ n_tiles, int top,
                    int Nout, int K, bf16* __restrict__ out_act, float* __restrict__ out_y, float limit, float alpha) {
     constexpr int NB = MODE == 0 ? 2 : 1;
@@ -315,8 +333,8 @@ moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, cons
     if (tid < GG_TM) srow[tid] = tid < rows ? sorted[r0 + tid] : -1;
     __syncthreads();
     const bf16* Bp[NB];
-    Bp[0] = B0 + (size_t)e * Nout * K;
-    if (MODE == 0) Bp[NB - 1] = B1 + (size_t)e * Nout * K;
+    Bp[0] = B0 + (size_t)e * b_stride;
+    if (MODE == 0) Bp[NB - 1] = B1 + (size_t)e * b_stride;
     // each thread copies chunks (row = c / 4, 8 k-values at (c % 4) * 8) c = tid and tid + 128 of every 64 x 32 tile
     auto load = [&](int stage, int k0) {
 #pragma unroll
@@ -391,7 +409,8 @@ moe_grouped_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B0, cons
 }
 
 // ids (N, top); sorted, offsets, tiles, n_tiles: int scratch of P, E + 1, 3 max_tiles and 1 values; act (P, F) bf16
-MB_API int mb_moe_grouped_bf16(const void* h, const int* ids, const void* wg, const void* wu, const void* wd, float* y,
+MB_API int mb_moe_grouped_bf16(const void* h, const int* ids, const void* wg, const void* wu, long long gu_stride,
+                               const void* wd, float* y,
                                void* act, int* sorted, int* offsets, int* tiles, int* n_tiles, int N, int D, int F, int E,
                                int top, float limit, float alpha, cudaStream_t st) {
     if (N == 0) return 0;
@@ -401,10 +420,91 @@ MB_API int mb_moe_grouped_bf16(const void* h, const int* ids, const void* wg, co
     moe_sort_kernel<<<1, 1024, (size_t)(3 * E + 2) * sizeof(int), st>>>(ids, (int)P, E, offsets, sorted, tiles, n_tiles, max_tiles);
     MB_LAUNCH_CHECK();
     moe_grouped_kernel<0><<<dim3(max_tiles, (F + GG_TN - 1) / GG_TN), 128, 0, st>>>(
-        (const bf16*)h, (const bf16*)wg, (const bf16*)wu, sorted, tiles, n_tiles, top, F, D, (bf16*)act, nullptr, limit, alpha);
+        (const bf16*)h, (const bf16*)wg, (const bf16*)wu, gu_stride, sorted, tiles, n_tiles, top, F, D, (bf16*)act, nullptr,
+        limit, alpha);
     MB_LAUNCH_CHECK();
     moe_grouped_kernel<1><<<dim3(max_tiles, (D + GG_TN - 1) / GG_TN), 128, 0, st>>>(
-        (const bf16*)act, (const bf16*)wd, nullptr, sorted, tiles, n_tiles, top, D, F, nullptr, y, limit, alpha);
+        (const bf16*)act, (const bf16*)wd, nullptr, (long long)D * F, sorted, tiles, n_tiles, top, D, F, nullptr, y, limit,
+        alpha);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Steps of 128 tokens and more (bf16) hand the two products to the tcgen05 product in its grouped form, which wants the
+// rows of every expert side by side, starting at a multiple of 128:
+//   moe_sort_padded   one block: per pair its row in that layout (`place`), per tile of 128 rows its expert (-1: empty)
+//   moe_gather_rows   h rows, by token, to their places
+//   moe_combine_rows  out[n] = sum over the places, in order, of weight * y[place of (n, k)]
+__global__ void moe_sort_padded_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ place,
+                                       int* __restrict__ tile_expert, int max_tiles) {
+    extern __shared__ int sh[];
+    int* cnt = sh;              // E
+    int* start = sh + E;        // E + 1, in tiles
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        int e = ids[p];
+        if (e < 0 || e >= E) e = 0;
+        atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int e = 0; e < E; e++) { start[e] = t; t += (cnt[e] + 127) / 128; }
+        start[E] = t;
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        for (int t = start[e]; t < start[e + 1] && t < max_tiles; t++) tile_expert[t] = e;
+        cnt[e] = start[e] * 128;                    // from here on: the next free row of the expert
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        int e = ids[p];
+        if (e < 0 || e >= E) e = 0;
+        place[p] = atomicAdd(&cnt[e], 1);
+    }
+}
+
+__global__ void moe_gather_rows_kernel(const bf16* __restrict__ h, const int* __restrict__ place, bf16* __restrict__ rows, int D,
+                                       int top) {
+    const int p = blockIdx.x;
+    const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(p / top) * D);
+    uint4* dst = reinterpret_cast<uint4*>(rows + (size_t)place[p] * D);
+    for (int i = threadIdx.x; i < D / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void moe_combine_rows_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ wts,
+                                        bf16* __restrict__ out, int D, int top) {
+    const int n = blockIdx.x;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int kk = 0; kk < top; kk++) acc = fmaf(wts[(size_t)n * top + kk], y[(size_t)place[(size_t)n * top + kk] * D + d], acc);
+        out[(size_t)n * D + d] = __float2bfloat16_rn(acc);
+    }
+}
+
+// place (N top), tile_expert (N top / 128 + E), rows ((N top / 128 + E) 128, D) bf16
+MB_API int mb_moe_sort_gather(const void* h, const int* ids, int* place, int* tile_expert, void* rows, int N, int D, int E,
+                              int top, cudaStream_t st) {
+    if (N == 0) return 0;
+    const long long P = (long long)N * top;
+    if (D % 8 || D < 8 || E < 1 || E > 4096 || P > (1 << 24)) return -2;
+    const int max_tiles = (int)(P / 128) + E;
+    moe_sort_padded_kernel<<<1, 1024, (size_t)(2 * E + 1) * sizeof(int), st>>>(ids, (int)P, E, place, tile_expert, max_tiles);
+    MB_LAUNCH_CHECK();
+    moe_gather_rows_kernel<<<(unsigned)P, 128, 0, st>>>((const bf16*)h, place, (bf16*)rows, D, top);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+
+MB_API int mb_moe_combine_rows(const float* y, const int* place, const float* wts, void* out, int N, int D, int top,
+                               cudaStream_t st) {
+    if (N == 0) return 0;
+    moe_combine_rows_kernel<<<N, 256, 0, st>>>(y, place, wts, (bf16*)out, D, top);
     MB_LAUNCH_CHECK();
     return 0;
 }

@@ -407,15 +407,27 @@ def moe_select(z, correction, ids, wts, groups=1, keep=1):
     _check(f(_p(z), _p(correction), _p(ids), _p(wts), N, E, ids.shape[1], int(groups), int(keep), _stream()), "moe_select")
 
 
-def moe_experts(h, ids, wg, wu, wd, y, limit, alpha):
+def _expert_views(wg, wu, wd):
+    D = wg.shape[2]
+    if (wg.stride(1), wg.stride(2)) != (D, 1) or wu.stride() != wg.stride() or not wd.is_contiguous():
+        raise KernelError("the experts' matrices must have contiguous rows, gate and up alike")
+
+
+def moe_experts(h, ids, wg, wu, wd, y, limit, alpha, act=None):
     """y[n, k] = Wd[e] (g sigmoid(alpha g) (u + 1)), g = min(Wg[e] h[n], limit), u = clamp(Wu[e] h[n], -limit, limit),
-    e = ids[n, k].  h (N, D); wg, wu (E, F, D); wd (E, D, F); y (N, top, D) float32"""
-    _cuda(h, ids, wg, wu, wd, y)
+    e = ids[n, k].  h (N, D); wg, wu (E, F, D), whole tensors or the two halves of one (E, 2F, D) tensor; wd (E, D, F);
+    y (N, top, D) float32; act (N * top, F) float32: working memory (made here when not given)"""
+    _cuda(h, ids, wg, wu, wd, y, act)
     N, D = h.shape
     E, F, _ = wg.shape
-    f = _fn("moe", "mb_moe_experts_" + _suffix(h.dtype), [c_void_p] * 6 + [c_int] * 5 + [c_float, c_float, c_void_p])
-    _check(f(_p(h), _p(ids), _p(wg), _p(wu), _p(wd), _p(y), N, D, F, E, ids.shape[1], float(limit), float(alpha),
-             _stream()), "moe_experts")
+    _expert_views(wg, wu, wd)
+    if act is None:
+        act = torch.empty((N * ids.shape[1], F), dtype=torch.float32, device=h.device)
+    f = _fn("moe", "mb_moe_experts_" + _suffix(h.dtype),
+            [c_void_p] * 4 + [c_ll] + [c_void_p] * 3 + [c_int] * 5 + [c_float, c_float, c_void_p])
+    _check(f(_p(h), _p(ids), _p(wg), _p(wu), wg.stride(0), _p(wd), _p(y), _p(act), N, D, F, E, ids.shape[1], float(limit),
+             float(alpha), _stream()), "moe_experts")
+    COUNTERS["launches"] += 1
 
 
 # Steps of more tokens than this run the experts on tensor-core tiles over the pairs sorted by expert (bf16 only).
@@ -447,10 +459,47 @@ def moe_grouped(h, ids, wg, wu, wd, y, act, scratch, limit, alpha):
     sorted_, offsets = scratch[:P], scratch[P:P + E + 1]
     tiles = scratch[P + E + 1:P + E + 1 + 3 * max_tiles]
     n_tiles = scratch[P + E + 1 + 3 * max_tiles:]
-    f = _fn("moe", "mb_moe_grouped_bf16", [c_void_p] * 11 + [c_int] * 5 + [c_float, c_float, c_void_p])
-    _check(f(_p(h), _p(ids), _p(wg), _p(wu), _p(wd), _p(y), _p(act), _p(sorted_), _p(offsets), _p(tiles), _p(n_tiles), N, D,
-             F, E, top, float(limit), float(alpha), _stream()), "moe_grouped")
+    _expert_views(wg, wu, wd)
+    f = _fn("moe", "mb_moe_grouped_bf16", [c_void_p] * 4 + [c_ll] + [c_void_p] * 7 + [c_int] * 5 + [c_float, c_float, c_void_p])
+    _check(f(_p(h), _p(ids), _p(wg), _p(wu), wg.stride(0), _p(wd), _p(y), _p(act), _p(sorted_), _p(offsets), _p(tiles),
+             _p(n_tiles), N, D, F, E, top, float(limit), float(alpha), _stream()), "moe_grouped")
     COUNTERS["launches"] += 2
+
+
+def moe_tc5_supports(N, D, F, dtype):
+    """steps of 128 tokens and more: the experts' products run on the tcgen05 product in its grouped form"""
+    return dtype == torch.bfloat16 and N >= 128 and D % 8 == 0 and F % 8 == 0 and TC5["experts"]
+
+
+def moe_tc5_tiles(N, top, E):
+    """-> the number of tiles of 128 rows the sorted layout has room for (every expert's rows start at a multiple of 128)"""
+    return N * top // 128 + E
+
+
+def moe_tc5(h, ids, wts, wgu, wd, out, rows, act, y, scratch, limit, alpha):
+    """The routed experts of a step of many tokens, bf16: ids (N, top) and wts from moe_select; wgu (E, 2F, D), every
+    expert's gate rows then its up rows; wd (E, D, F); out (N, D).  Working memory, with T = moe_tc5_tiles(N, top, E):
+    rows (128 T, D) bf16, act (128 T, F) bf16, y (128 T, D) float32, scratch (N top + T) int32."""
+    _cuda(h, ids, wts, wgu, wd, out, rows, act, y, scratch)
+    N, D = h.shape
+    E, F = wgu.shape[0], wgu.shape[1] // 2
+    top = ids.shape[1]
+    T = moe_tc5_tiles(N, top, E)
+    if rows.shape[0] < 128 * T or act.shape[0] < 128 * T or y.shape[0] < 128 * T or scratch.numel() < N * top + T:
+        raise KernelError("moe_tc5: the working memory is too small")
+    place, tile_expert = scratch[:N * top], scratch[N * top:N * top + T]
+    f = _fn("moe", "mb_moe_sort_gather", [c_void_p] * 5 + [c_int] * 4 + [c_void_p])
+    _check(f(_p(h), _p(ids), _p(place), _p(tile_expert), _p(rows), N, D, E, top, _stream()), "moe_sort_gather")
+    err = error_word(h.device)
+    f = _fn("gemm_tc5", "mb_gemm_tc5_grouped_gated_bf16",
+            [c_void_p] * 3 + [c_int] * 3 + [c_void_p, c_int, c_float, c_float, c_void_p, c_void_p])
+    _check(f(_p(rows), _p(wgu), _p(act), 128 * T, F, D, _p(tile_expert), E, float(limit), float(alpha), _p(err), _stream()),
+           "gemm_tc5_grouped_gated")
+    f = _fn("gemm_tc5", "mb_gemm_tc5_grouped_f32out", [c_void_p] * 3 + [c_int] * 3 + [c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_p(act), _p(wd), _p(y), 128 * T, D, F, _p(tile_expert), E, _p(err), _stream()), "gemm_tc5_grouped")
+    f = _fn("moe", "mb_moe_combine_rows", [c_void_p] * 4 + [c_int] * 3 + [c_void_p])
+    _check(f(_p(y), _p(place), _p(wts), _p(out), N, D, top, _stream()), "moe_combine_rows")
+    COUNTERS["launches"] += 1
 
 
 def moe_combine(y, wts, out):
@@ -506,7 +555,7 @@ def linear(a, w, out=None, out_dtype=None):
 # The package's own tcgen05 product for prompt portions (128 tokens or more).  "swiglu": the fused gate/up product
 # (measured 317 us against 310 + 33 us for the library product and the separate gate kernel at 2,048 tokens of the
 # Llama-3.1-8B shape); "plain": every product (87 to 97 % of the library's speed, so off by default).
-TC5 = {"swiglu": True, "plain": False}
+TC5 = {"swiglu": True, "plain": False, "experts": True}
 
 
 def tc5_supports(N, M, K, mode="plain"):

@@ -54,7 +54,9 @@ class RoutedExperts:
         self.wr = tensors[self.n["router"]]
         self.corr = tensors[self.n["correction"]] if self.has_correction else None
         stack = lambda which: torch.stack([tensors[self._expert(e, which)] for e in range(self.E)], 0).contiguous()
-        self.wg, self.wu, self.wd = stack("gate"), stack("up"), stack("down")
+        # (E, 2F, D): every expert's gate rows, then its up rows; the kernels that want them apart take views
+        self.wgu = torch.cat([stack("gate"), stack("up")], 1).contiguous()
+        self.wg, self.wu, self.wd = self.wgu[:, :self.F], self.wgu[:, self.F:], stack("down")
 
     def forward(self, ctx, h, out="delta"):
         import torch
@@ -64,6 +66,16 @@ class RoutedExperts:
         ids = ctx.ws.get("router_ids", N, (self.top,), torch.int32)
         wts = ctx.ws.get("router_weights", N, (self.top,), torch.float32)
         ops.moe_select(z, self.corr, ids, wts, self.groups, self.keep)
+        if ops.moe_tc5_supports(N, self.D, self.F, ctx.dtype) and not ctx.options.get("plain_experts", False):
+            T = ops.moe_tc5_tiles(ctx.ws.max_rows, self.top, self.E)
+            rows = ctx.ws.get("expert_rows", 128 * T, (self.D,), ctx.dtype, reserve=128 * T)
+            act = ctx.ws.get("expert_rows_act", 128 * T, (self.F,), ctx.dtype, reserve=128 * T)
+            y = ctx.ws.get("expert_rows_out", 128 * T, (self.D,), torch.float32, reserve=128 * T)
+            scratch = ctx.ws.get("expert_places", ctx.ws.max_rows * self.top + T, (), torch.int32,
+                                 reserve=ctx.ws.max_rows * self.top + T)
+            delta = ctx.ws.get(out, N, (self.D,), ctx.dtype)
+            ops.moe_tc5(h, ids, wts, self.wgu, self.wd, delta, rows, act, y, scratch, self.limit, self.alpha)
+            return delta, None
         y = ctx.ws.get("expert_out", N, (self.top, self.D), torch.float32)
         if ops.moe_grouped_supports(N, self.D, self.F, ctx.dtype) and not ctx.options.get("plain_experts", False):
             act = ctx.ws.get("expert_act", N * self.top, (self.F,), ctx.dtype, reserve=ctx.ws.max_rows * self.top)
@@ -71,7 +83,10 @@ class RoutedExperts:
             scratch = ctx.ws.get("expert_sort", max(n, ops.moe_grouped_scratch(N, self.top, self.E)), (), torch.int32, reserve=n)
             ops.moe_grouped(h, ids, self.wg, self.wu, self.wd, y, act, scratch, self.limit, self.alpha)
         else:
-            ops.moe_experts(h, ids, self.wg, self.wu, self.wd, y, self.limit, self.alpha)
+            # bfloat16 steps of many tokens take the other form: room for the few
+            most = min(ctx.ws.max_rows, max(N, ops.MOE_GROUPED["tokens"])) if ctx.dtype == torch.bfloat16 else ctx.ws.max_rows
+            act = ctx.ws.get("expert_act_few", N * self.top, (self.F,), torch.float32, reserve=most * self.top)
+            ops.moe_experts(h, ids, self.wg, self.wu, self.wd, y, self.limit, self.alpha, act)
         delta = ctx.ws.get(out, N, (self.D,), ctx.dtype)
         ops.moe_combine(y, wts, delta)
         return delta, None

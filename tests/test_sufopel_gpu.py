@@ -169,6 +169,38 @@ def test_experts_on_tensor_core_tiles(D, F, N, E, top):
     kernel_close(y2, want, "bfloat16", "experts pair by pair", 5e-3)
 
 
+@pytest.mark.parametrize("D,F,N,E,top", [(64, 128, 300, 5, 2), (96, 72, 128, 7, 3), (256, 200, 515, 9, 4)])
+def test_experts_on_the_tcgen05_product(D, F, N, E, top):
+    """every expert's rows side by side from a multiple of 128 on; experts with hundreds of rows, with a few, with none;
+    feature tiles that reach beyond an expert's rows into the next expert's"""
+    from mashbox_b200 import ops
+    g = torch.Generator().manual_seed(F)
+    limit, bf = 1.1, torch.bfloat16
+    h = rnd(g, N, D, dtype="bfloat16")
+    wg, wu, wd = (rnd(g, E, a, b, dtype="bfloat16", scale=0.3) for a, b in ((F, D), (F, D), (D, F)))
+    ids = torch.stack([torch.randperm(E - 1, generator=g)[:top] for _ in range(N)])         # the last expert gets nobody
+    ids[::2, 0] = ids[0, 0]                                                                  # one expert gets half the rows
+    for n in range(N):                                                                       # ... and no row twice
+        if (ids[n, 1:] == ids[n, 0]).any():
+            ids[n] = torch.randperm(E - 1, generator=g)[:top]
+    wts = torch.rand(N, top, generator=g).double()
+    T = ops.moe_tc5_tiles(N, top, E)
+    dev = lambda t: t.to(DEV, bf).contiguous()
+    out = torch.empty(N, D, device=DEV, dtype=bf)
+    rows, act = torch.empty(128 * T, D, device=DEV, dtype=bf), torch.empty(128 * T, F, device=DEV, dtype=bf)
+    y, scratch = torch.empty(128 * T, D, device=DEV), torch.empty(N * top + T, dtype=torch.int32, device=DEV)
+    ops.moe_tc5(dev(h), ids.int().to(DEV), wts.float().to(DEV), dev(torch.cat([wg, wu], 1)), dev(wd), out, rows, act, y,
+                scratch, limit, 1.702)
+    ops.check_error_word(ops.error_word(DEV))
+    hh = h[:, None, :].expand(N, top, D)
+    r = lambda t: t.to(bf).double()
+    gg = torch.clamp(r(torch.einsum("nkd,nkfd->nkf", hh, wg[ids])), max=limit)
+    uu = torch.clamp(r(torch.einsum("nkd,nkfd->nkf", hh, wu[ids])), -limit, limit)
+    a = r(gg * torch.sigmoid(1.702 * gg) * (uu + 1.0))
+    want = (torch.einsum("nkf,nkdf->nkd", a, wd[ids]) * wts[:, :, None]).sum(1)
+    kernel_close(out, want, "bfloat16", "experts on the tcgen05 product", 1e-2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_row_kernels(dtype):
     """learned positions, the norm of a sublayer's output with the next norm, the token's own input, the per-head
