@@ -832,6 +832,10 @@ def sufopel_kernels(a, z, P, B, ctx, pk):
         r = mem(us, 2 * S * H * dim * dim * 4 + N * H * dim * 5 * 4)
         r["gflops_fp32"] = N * H * dim * dim * 7 / us / 1e3                 # decay, two dot products, update: 7 per element
         res[f"delta_rule_{form}"] = r
+        for lanes in (16, 32):                                                # the same with more threads a column
+            ops.delta_rule_lanes(lanes)
+            res[f"delta_rule_{form}"][f"us_{lanes}_lanes"] = timed(lambda: ops.delta_rule(q, k, v, g, beta, o, state, seq, H, H, dim, dim))
+        ops.delta_rule_lanes(0)
     # ---- Llama's attention at equal heads, beside it: P prompt tokens; B tokens over ctx keys
     att = PagedAttention(H, max(1, H // 4), dim)
     lat = PagedAttention(H, 1, R, None, dim ** -0.5)
@@ -863,7 +867,19 @@ def sufopel_kernels(a, z, P, B, ctx, pk):
             act = torch.empty(N * top, F, device=dev, dtype=torch.bfloat16)
             scratch = torch.empty(ops.moe_grouped_scratch(N, top, E), dtype=torch.int32, device=dev)
             us = timed(lambda: ops.moe_grouped(h, ids, wg, wu, wd, y, act, scratch, 7.0, 1.702))
+            res["experts_prompt_mma_sync"] = mat(us, 2 * N * top * 3 * F * D)
+            T = ops.moe_tc5_tiles(N, top, E)
+            wts, out = torch.rand(N, top, generator=gen, device=dev), torch.empty(N, D, device=dev, dtype=torch.bfloat16)
+            rows, act2 = torch.empty(128 * T, D, device=dev, dtype=torch.bfloat16), torch.empty(128 * T, F, device=dev, dtype=torch.bfloat16)
+            y2, places = torch.empty(128 * T, D, device=dev), torch.empty(N * top + T, dtype=torch.int32, device=dev)
+            wgu2 = torch.cat([wg, wu], 1).contiguous()
+            us = timed(lambda: ops.moe_tc5(h, ids, wts, wgu2, wd, out, rows, act2, y2, places, 7.0, 1.702))
             res["experts_prompt"] = mat(us, 2 * N * top * 3 * F * D)
+            # few rows an expert: every expert's matrices have to be read once, which may take longer than the products
+            touched = len(set(ids.flatten().tolist()))
+            need = max(2 * N * top * 3 * F * D / (pk["bf16_tflops"] * 1e6), touched * 3 * F * D * 2 / (pk["hbm_gbs"] * 1e3))
+            res["experts_prompt"].update(weights_gbs=touched * 3 * F * D * 2 / us / 1e3, frac_of_roofline=need / us)
+            del wgu2
             wgu, wdn, a1, o1 = bf(2 * F * top, D), bf(D, F * top), torch.empty(N, F * top, device=dev, dtype=torch.bfloat16), torch.empty(N, D, device=dev, dtype=torch.bfloat16)
             us = timed(lambda: (ops.linear_swiglu(h, wgu, a1), ops.linear(a1, wdn, out=o1)))
             res["feed_forward_llama_prompt"] = mat(us, 2 * N * top * 3 * F * D)

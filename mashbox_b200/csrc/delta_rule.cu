@@ -4,9 +4,9 @@
 //     S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
 // Column c of S (the dim values that belong to value channel c) never meets another column: S^T k and S^T q are dot
 // products along a column, and the update adds k times the column's own u.  So a column is the unit of work: LANES
-// threads hold it in registers, dim / LANES values each, the two dot products are partial sums (four chains a thread,
-// added pairwise) met by shuffles, and a block of 16 columns walks a sequence's tokens in order, reading the token's q,
-// k, g (shared by all columns), v and beta from shared memory, BATCH tokens per block barrier.  A prompt of any length, a
+// threads hold it in registers, four values each (eight for the widest keys), the two dot products are partial sums
+// (four chains a thread, added pairwise) met by shuffles, and a block of a few columns walks a sequence's tokens in
+// order, reading the token's q, k, g (shared by all columns), v and beta from shared memory, BATCH tokens per barrier.  A prompt of any length, a
 // portion and a single decoded token are the same loop; the state is read once and written once per step.  Every sum
 // runs in a fixed order, so the result does not depend on how a prompt was cut into steps.
 //
@@ -16,11 +16,14 @@
 //   gated_rms     o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) per head, to the storage type
 #include "common.cuh"
 
-#define DR_LANES 8
-#define DR_COLS 16
+#define DR_THREADS 256
 #define DR_BATCH 8
+#define DR_STAGES 4
 
 // 4 bytes from global to shared memory without a register in between; size 0: the destination is set to zero
+__device__ __forceinline__ void dr_cp16(float* smem, const float* gmem, int size) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(size));
+}
 __device__ __forceinline__ void dr_cp4(float* smem, const float* gmem, int size) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(size));
 }
@@ -62,21 +65,31 @@ __global__ void delta_gates_kernel(const T* __restrict__ qkv, const T* __restric
     if (threadIdx.x == 0) beta[(size_t)n * H + h] = dr_sigmoid(mb_load(low + (size_t)n * low_stride + h));
 }
 
-// grid (column tiles, H, sequences), DR_COLS * DR_LANES threads.  R: state values per thread (a multiple of 4),
-// dim <= R * DR_LANES = DP.  Thread (column, lane) holds channels r4 * 4 DR_LANES + lane * 4 + c (r4 < R / 4, c < 4), so
-// that its reads of a token's q, k, g are 16-byte loads and the lanes of a column read one contiguous stretch.  The
-// next DR_BATCH tokens are sent for (cp.async, zero fill beyond dim and vdim) while the current ones are worked on.
-template <int R>
-__global__ void __launch_bounds__(DR_COLS * DR_LANES)
+// grid (column tiles, H, sequences), DR_THREADS threads: COLS = DR_THREADS / LANES columns a block.  LANES threads hold
+// a column, 4 R4 values each: thread (column, lane) holds channels r4 * 4 LANES + lane * 4 + c (r4 < R4, c < 4), so that
+// its reads of a token's q, k, g are 16-byte loads and the lanes of a column read one contiguous stretch;
+// dim <= 4 R4 LANES = DP.  As many lanes as the key size allows (a whole warp from 128 on): a sequence gives
+// heads x vdim x LANES threads, and one warp a scheduler cannot hide the latency of its own shared-memory reads and
+// shuffles.  The next BT tokens are sent for (cp.async, zero fill beyond dim and vdim) while the current ones are
+// worked on.
+template <int LANES, int R4>
+__global__ void __launch_bounds__(DR_THREADS)
 delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ g, const float* __restrict__ beta, float* __restrict__ o,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
                   const int* __restrict__ q_len, const int* __restrict__ state_slot, int H, int G, int dim, int vdim) {
-    constexpr int DP = R * DR_LANES, R4 = R / 4, BT = R >= 32 ? DR_BATCH / 2 : DR_BATCH;
-    __shared__ __align__(16) float sq[2][BT][DP], sk[2][BT][DP], sg[2][BT][DP];
-    __shared__ float sv[2][BT][DR_COLS], sb[2][BT];
-    const int s = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * DR_COLS;
-    const int lane = threadIdx.x & (DR_LANES - 1), cl = threadIdx.x / DR_LANES, col = col0 + cl;
+    constexpr int DP = 4 * R4 * LANES, R = 4 * R4, COLS = DR_THREADS / LANES, BT = DR_BATCH, CP = COLS < 4 ? 4 : COLS;
+    // a ring of DR_STAGES stages of BT tokens: the inputs come from DRAM, a microsecond or two away, and a stage is worked
+    // through in a fraction of that
+    extern __shared__ __align__(16) float ring[];
+    typedef float (*RowsDP)[BT][DP];
+    typedef float (*RowsCP)[BT][CP];
+    typedef float (*RowsB)[BT];
+    RowsDP sq = reinterpret_cast<RowsDP>(ring), sk = sq + DR_STAGES, sg = sk + DR_STAGES;
+    RowsCP sv = reinterpret_cast<RowsCP>(ring + 3 * DR_STAGES * BT * DP);
+    RowsB sb = reinterpret_cast<RowsB>(ring + 3 * DR_STAGES * BT * DP + DR_STAGES * BT * CP);
+    const int s = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * COLS;
+    const int lane = threadIdx.x & (LANES - 1), cl = threadIdx.x / LANES, col = col0 + cl;
     const bool live = col < vdim;
     const int a = q_start[s], len = q_len[s], j = h / (H / G);
     float* S = state + (size_t)state_slot[s] * state_stride + (size_t)h * dim * vdim;
@@ -85,57 +98,80 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     for (int r4 = 0; r4 < R4; r4++)
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            const int i = r4 * 4 * DR_LANES + lane * 4 + c;
+            const int i = r4 * 4 * LANES + lane * 4 + c;
             st[r4 * 4 + c] = (live && i < dim) ? S[(size_t)i * vdim + col] : 0.0f;
         }
+    // 16 bytes a copy where every row starts on a 16-byte boundary (dim and vdim multiples of 4), else 4
+    const bool vec = (dim & 3) == 0 && (vdim & 3) == 0 && COLS >= 4;
     auto fetch = [&](int buf, int t0) {
         const int nb = min(BT, len - t0);
-        for (int idx = threadIdx.x; idx < nb * DP; idx += blockDim.x) {
-            const int tt = idx / DP, i = idx - tt * DP;
-            const size_t n = (size_t)(a + t0 + tt);
-            const int sz = i < dim ? 4 : 0;
-            const int ii = i < dim ? i : 0;
-            dr_cp4(&sq[buf][tt][i], q + (n * G + j) * dim + ii, sz);
-            dr_cp4(&sk[buf][tt][i], k + (n * G + j) * dim + ii, sz);
-            dr_cp4(&sg[buf][tt][i], g + (n * H + h) * dim + ii, sz);
-        }
-        for (int idx = threadIdx.x; idx < nb * DR_COLS; idx += blockDim.x) {
-            const int tt = idx / DR_COLS, c = idx - tt * DR_COLS;
-            const bool in = col0 + c < vdim;
-            dr_cp4(&sv[buf][tt][c], v + ((size_t)(a + t0 + tt) * H + h) * vdim + (in ? col0 + c : 0), in ? 4 : 0);
+        if (vec) {
+            for (int idx = threadIdx.x; idx < nb * (DP / 4); idx += DR_THREADS) {
+                const int tt = idx / (DP / 4), i = (idx - tt * (DP / 4)) * 4;
+                const size_t n = (size_t)(a + t0 + tt);
+                const int sz = i < dim ? 16 : 0;
+                const int ii = i < dim ? i : 0;
+                dr_cp16(&sq[buf][tt][i], q + (n * G + j) * dim + ii, sz);
+                dr_cp16(&sk[buf][tt][i], k + (n * G + j) * dim + ii, sz);
+                dr_cp16(&sg[buf][tt][i], g + (n * H + h) * dim + ii, sz);
+            }
+            for (int idx = threadIdx.x; idx < nb * (COLS / 4); idx += DR_THREADS) {
+                const int tt = idx / (COLS / 4), c = (idx - tt * (COLS / 4)) * 4;
+                const bool in = col0 + c < vdim;
+                dr_cp16(&sv[buf][tt][c], v + ((size_t)(a + t0 + tt) * H + h) * vdim + (in ? col0 + c : 0), in ? 16 : 0);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < nb * DP; idx += DR_THREADS) {
+                const int tt = idx / DP, i = idx - tt * DP;
+                const size_t n = (size_t)(a + t0 + tt);
+                const int sz = i < dim ? 4 : 0;
+                const int ii = i < dim ? i : 0;
+                dr_cp4(&sq[buf][tt][i], q + (n * G + j) * dim + ii, sz);
+                dr_cp4(&sk[buf][tt][i], k + (n * G + j) * dim + ii, sz);
+                dr_cp4(&sg[buf][tt][i], g + (n * H + h) * dim + ii, sz);
+            }
+            for (int idx = threadIdx.x; idx < nb * COLS; idx += DR_THREADS) {
+                const int tt = idx / COLS, c = idx - tt * COLS;
+                const bool in = col0 + c < vdim;
+                dr_cp4(&sv[buf][tt][c], v + ((size_t)(a + t0 + tt) * H + h) * vdim + (in ? col0 + c : 0), in ? 4 : 0);
+            }
         }
         if (threadIdx.x < nb) dr_cp4(&sb[buf][threadIdx.x], beta + (size_t)(a + t0 + threadIdx.x) * H + h, 4);
         asm volatile("cp.async.commit_group;\n" ::);
     };
-    if (len > 0) fetch(0, 0);
+    // every iteration commits one group (an empty one beyond the end), so the group of the stage that is worked on
+    // next is always the (DR_STAGES - 1)-th from the newest
+    for (int p = 0; p < DR_STAGES - 1; p++) {
+        if (p * BT < len) fetch(p, p * BT);
+        else asm volatile("cp.async.commit_group;\n" ::);
+    }
     for (int t0 = 0, it = 0; t0 < len; t0 += BT, it++) {
-        const int nb = min(BT, len - t0), buf = it & 1;
-        if (t0 + BT < len) {
-            fetch(buf ^ 1, t0 + BT);
-            asm volatile("cp.async.wait_group 1;\n" ::);
-        } else {
-            asm volatile("cp.async.wait_group 0;\n" ::);
-        }
+        const int nb = min(BT, len - t0), buf = it % DR_STAGES;
+        const int ahead = t0 + (DR_STAGES - 1) * BT;
+        if (ahead < len) fetch((it + DR_STAGES - 1) % DR_STAGES, ahead);      // the stage worked on last iteration is free
+        else asm volatile("cp.async.commit_group;\n" ::);
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(DR_STAGES - 1));
         __syncthreads();
+#pragma unroll 2
         for (int tt = 0; tt < nb; tt++) {
             float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
             float4 kk[R4];
 #pragma unroll
             for (int r4 = 0; r4 < R4; r4++) {
-                const float4 gg = *reinterpret_cast<const float4*>(&sg[buf][tt][r4 * 4 * DR_LANES + lane * 4]);
-                kk[r4] = *reinterpret_cast<const float4*>(&sk[buf][tt][r4 * 4 * DR_LANES + lane * 4]);
+                const float4 gg = *reinterpret_cast<const float4*>(&sg[buf][tt][r4 * 4 * LANES + lane * 4]);
+                kk[r4] = *reinterpret_cast<const float4*>(&sk[buf][tt][r4 * 4 * LANES + lane * 4]);
                 st[r4 * 4 + 0] *= gg.x; st[r4 * 4 + 1] *= gg.y; st[r4 * 4 + 2] *= gg.z; st[r4 * 4 + 3] *= gg.w;
                 d0 = fmaf(st[r4 * 4 + 0], kk[r4].x, d0); d1 = fmaf(st[r4 * 4 + 1], kk[r4].y, d1);
                 d2 = fmaf(st[r4 * 4 + 2], kk[r4].z, d2); d3 = fmaf(st[r4 * 4 + 3], kk[r4].w, d3);
             }
             float dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
-            for (int m = 1; m < DR_LANES; m <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
+            for (int m = 1; m < LANES; m <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
             const float u = sb[buf][tt] * (sv[buf][tt][cl] - dot);
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
             for (int r4 = 0; r4 < R4; r4++) {
-                const float4 qq = *reinterpret_cast<const float4*>(&sq[buf][tt][r4 * 4 * DR_LANES + lane * 4]);
+                const float4 qq = *reinterpret_cast<const float4*>(&sq[buf][tt][r4 * 4 * LANES + lane * 4]);
                 st[r4 * 4 + 0] = fmaf(kk[r4].x, u, st[r4 * 4 + 0]); st[r4 * 4 + 1] = fmaf(kk[r4].y, u, st[r4 * 4 + 1]);
                 st[r4 * 4 + 2] = fmaf(kk[r4].z, u, st[r4 * 4 + 2]); st[r4 * 4 + 3] = fmaf(kk[r4].w, u, st[r4 * 4 + 3]);
                 a0 = fmaf(st[r4 * 4 + 0], qq.x, a0); a1 = fmaf(st[r4 * 4 + 1], qq.y, a1);
@@ -143,7 +179,7 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
             }
             float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
-            for (int m = 1; m < DR_LANES; m <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+            for (int m = 1; m < LANES; m <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
             if (lane == 0 && live) o[((size_t)(a + t0 + tt) * H + h) * vdim + col] = acc;
         }
         __syncthreads();
@@ -152,7 +188,7 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     for (int r4 = 0; r4 < R4; r4++)
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            const int i = r4 * 4 * DR_LANES + lane * 4 + c;
+            const int i = r4 * 4 * LANES + lane * 4 + c;
             if (live && i < dim) S[(size_t)i * vdim + col] = st[r4 * 4 + c];
         }
 }
@@ -200,20 +236,33 @@ MB_API int mb_delta_gates_bf16(const void* qkv, const void* low, int low_stride,
                                     v, g, beta, N, H, G, dim, vdim, unit_eps, st);
 }
 
+// threads per column: 0 = as few as hold the keys at four values a thread; 8, 16 or 32 = that many (more values a thread)
+static int dr_lanes = 0;
+MB_API int mb_delta_rule_set_lanes(int lanes) { dr_lanes = lanes; return 0; }
+
 MB_API int mb_delta_rule(const float* q, const float* k, const float* v, const float* g, const float* beta, float* o,
                          float* state, long long state_stride, const int* q_start, const int* q_len, const int* state_slot,
                          int S, int H, int G, int dim, int vdim, cudaStream_t st) {
     if (S == 0) return 0;
-    if (G < 1 || H % G || H > 65535 || S > 65535 || dim < 1 || dim > 32 * DR_LANES || vdim < 1) return -2;
-    const dim3 grid((vdim + DR_COLS - 1) / DR_COLS, H, S), block(DR_COLS * DR_LANES);
-#define DR_CASE(R)                                                                                                         \
-    if (dim <= R * DR_LANES) {                                                                                             \
-        delta_rule_kernel<R><<<grid, block, 0, st>>>(q, k, v, g, beta, o, state, state_stride, q_start, q_len, state_slot, \
-                                                     H, G, dim, vdim);                                                     \
+    if (G < 1 || H % G || H > 65535 || S > 65535 || dim < 1 || dim > 256 || vdim < 1) return -2;
+#define DR_CASE(LANES, R4)                                                                                                 \
+    if (dim <= 4 * R4 * LANES && (lanes == 0 || lanes == LANES)) {                                                         \
+        const int cols = DR_THREADS / LANES, cp = cols < 4 ? 4 : cols;                                                     \
+        const size_t smem = (size_t)DR_STAGES * DR_BATCH * (3 * 4 * R4 * LANES + cp + 1) * sizeof(float);                  \
+        static bool configured = false;                                                                                    \
+        if (!configured && smem > 48 * 1024) {                                                                             \
+            cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<LANES, R4>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                 (int)smem);                                                               \
+            if (e != cudaSuccess) return (int)e;                                                                           \
+            configured = true;                                                                                             \
+        }                                                                                                                  \
+        delta_rule_kernel<LANES, R4><<<dim3((vdim + cols - 1) / cols, H, S), DR_THREADS, smem, st>>>(                      \
+            q, k, v, g, beta, o, state, state_stride, q_start, q_len, state_slot, H, G, dim, vdim);                        \
         MB_LAUNCH_CHECK();                                                                                                 \
         return 0;                                                                                                          \
     }
-    DR_CASE(4) DR_CASE(8) DR_CASE(16) DR_CASE(32)
+    const int lanes = dr_lanes;
+    DR_CASE(4, 1) DR_CASE(8, 1) DR_CASE(8, 2) DR_CASE(8, 4) DR_CASE(16, 1) DR_CASE(16, 2) DR_CASE(32, 1) DR_CASE(16, 4) DR_CASE(32, 2)
 #undef DR_CASE
     return -2;
 }

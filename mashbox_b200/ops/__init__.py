@@ -387,6 +387,14 @@ def delta_rule(q, k, v, g, beta, o, state, seq, H, G, dim, vdim):
              seq[0].shape[0], H, G, dim, vdim, _stream()), "delta_rule")
 
 
+def delta_rule_lanes(lanes):
+    """how many threads hold a column of the state: 0 = the default (8, with as many values each as the keys need),
+    16 or 32 = that many (fewer values a thread, more shuffles); a measuring switch"""
+    f = getattr(load_library("delta_rule"), "mb_delta_rule_set_lanes")
+    f.argtypes = [c_int]
+    f(int(lanes))
+
+
 def gated_rms(o, gate, w, out, H, vdim, eps):
     """out[n, h] = o[n, h] / sqrt(mean(o[n, h]^2) + eps) * w * sigmoid(gate[n, h]); o (N, H vdim) float32, gate a view
     (N, H vdim) of the activation dtype whose rows may be further apart, w (vdim,) float32, out the activation dtype"""

@@ -94,7 +94,11 @@ class PagedAttention:
         tiles = [1 if decode_form[s] else -(-ctx.q_len[s] * G // pre_rows) for s in range(S)]
         # the two forms are two launches: each is cut into splits by its own number of blocks
         base = {f: max(1, sum(t for t, d in zip(tiles, decode_form) if d == f) * KV) for f in (True, False)}
-        dec, pre, part_base, part_tok = [], [], [-1] * S, []
+        dec, pre, mid, part_base, part_tok = [], [], [], [-1] * S, []
+        # More query heads per kv head than a decode tile has rows (every head reads one row per position, say): a single
+        # token is already a prompt-form tile, which the tcgen05 kernel does not cut along the keys.  Such stretches of
+        # at most DECODE_ROWS tokens go to the TMA/mma prompt form with splits, in a list of their own.
+        wide = tc5 and G > DECODE_ROWS
 
         def key_tiles(s):
             hi = ctx.pos0[s] + ctx.q_len[s]
@@ -145,7 +149,8 @@ class PagedAttention:
                 for sp in range(cluster):
                     dec.append((0, s, 0, sp, cluster))
                 continue
-            if ctx.q_len[s] <= DECODE_ROWS and base[decode_form[s]] < target and (decode_form[s] or not tc5):
+            short = wide and not decode_form[s] and ctx.q_len[s] <= DECODE_ROWS
+            if ctx.q_len[s] <= DECODE_ROWS and base[decode_form[s]] < target and (decode_form[s] or not tc5 or short):
                 ns = max(1, min(max_splits, -(-target // base[decode_form[s]]), kv_tiles // 2))
                 ns = 1 << (ns.bit_length() - 1)                    # a power of two: few distinct work-list shapes
             if decode_form[s] and (crowd or ctx.options.get("attention_splits") is not None):
@@ -154,18 +159,20 @@ class PagedAttention:
                 part_base[s] = len(part_tok) // 2
                 for t in range(ctx.q_len[s]):
                     part_tok += [ctx.q_start[s] + t, ns]
-            dst = dec if decode_form[s] else pre
-            for m in range(tiles[s]):
+            dst = dec if decode_form[s] else (mid if short else pre)
+            rows = PREFILL_ROWS if short else pre_rows
+            for m in range(-(-ctx.q_len[s] * G // rows) if short else tiles[s]):
                 for sp in range(ns):
-                    dst.append((-(ctx.pos0[s] + (m + 1) * pre_rows // G), s, m, sp, ns))
+                    dst.append((-(ctx.pos0[s] + (m + 1) * rows // G), s, m, sp, ns))
         pre.sort()                                                  # the tiles with the most keys first
         name = "attn%d_" % len([k for k in ctx.memo if k[0] == "attention"])
         flat = lambda items: np.asarray([i[1:] for i in items], np.int32).reshape(-1)
         ctx.inputs.add(name + "dec", flat(dec))
         ctx.inputs.add(name + "pre", flat(pre))
+        ctx.inputs.add(name + "mid", flat(mid))
         ctx.inputs.add(name + "part_base", np.asarray(part_base, np.int32))
         ctx.inputs.add(name + "part_tok", np.asarray(part_tok, np.int32))
-        ctx.memo[key] = dict(name=name, n_dec=len(dec), n_pre=len(pre), n_part=len(part_tok) // 2,
+        ctx.memo[key] = dict(name=name, n_dec=len(dec), n_pre=len(pre), n_mid=len(mid), n_part=len(part_tok) // 2,
                              max_splits=max_splits, tc5=tc5, cluster=cluster)
 
     # ------------------------------------------------------------------------------------------ kernels
@@ -190,7 +197,7 @@ class PagedAttention:
             flash = ops.attention_tma if tma else ops.attention_mma
             # the TMA kernel merges the splits itself (the last block of a group does it); the other needs the merge kernel
             fused = (tma and n_part > 0 and ctx.options.get("attention_fused_merge", True)
-                     and ops.attention_tma_merges(max(plan["n_pre"], plan["n_dec"]), KV))
+                     and ops.attention_tma_merges(max(plan["n_pre"], plan["n_mid"], plan["n_dec"]), KV))
             extra = dict(merge=True) if fused else {}
             if rope is not None:
                 extra["rope"] = rope
@@ -199,7 +206,7 @@ class PagedAttention:
                                   ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev("seq_row"), table, H, KV, HD, page, pages,
                                   self.window, self.scale, ctx.err)
             for form, n_items, decode in ((nm + "pre", 0 if plan["tc5"] else plan["n_pre"], False),
-                                          (nm + "dec", plan["n_dec"], True)):
+                                          (nm + "mid", plan["n_mid"], False), (nm + "dec", plan["n_dec"], True)):
                 if n_items and decode and plan["cluster"]:
                     ops.attention_tma(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, True, ctx.dev("q_start"),
                                       ctx.dev("q_len"), ctx.dev("pos0"), None, ctx.dev("seq_row"), table, None, None, 1,
