@@ -16,7 +16,9 @@
 //   gated_rms     o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) per head, to the storage type
 #include "common.cuh"
 
-#define DR_THREADS 256
+#define DR_THREADS 128
+#define DR_CPT 1            // columns a thread (more: what it reads of q, k, g from shared memory serves them all, but a
+                            // sequence then gives fewer warps than the device has schedulers; 4 was slower at every size tried)
 #define DR_BATCH 8
 #define DR_STAGES 4
 
@@ -65,10 +67,10 @@ __global__ void delta_gates_kernel(const T* __restrict__ qkv, const T* __restric
     if (threadIdx.x == 0) beta[(size_t)n * H + h] = dr_sigmoid(mb_load(low + (size_t)n * low_stride + h));
 }
 
-// grid (column tiles, H, sequences), DR_THREADS threads: COLS = DR_THREADS / LANES columns a block.  LANES threads hold
-// a column, 4 R4 values each: thread (column, lane) holds channels r4 * 4 LANES + lane * 4 + c (r4 < R4, c < 4), so that
-// its reads of a token's q, k, g are 16-byte loads and the lanes of a column read one contiguous stretch;
-// dim <= 4 R4 LANES = DP.  As many lanes as the key size allows (a whole warp from 128 on): a sequence gives
+// grid (column tiles, H, sequences), DR_THREADS threads: DR_THREADS / LANES groups of LANES threads, each group DR_CPT
+// columns.  A thread holds 4 R4 values of each of its columns: channels r4 * 4 LANES + lane * 4 + c (r4 < R4, c < 4), so
+// that its reads of a token's q, k, g are 16-byte loads, the lanes of a group read one contiguous stretch, and every
+// value read serves DR_CPT columns; dim <= 4 R4 LANES = DP.  As many lanes as the key size allows (a whole warp from 128 on): a sequence gives
 // heads x vdim x LANES threads, and one warp a scheduler cannot hide the latency of its own shared-memory reads and
 // shuffles.  The next BT tokens are sent for (cp.async, zero fill beyond dim and vdim) while the current ones are
 // worked on.
@@ -78,31 +80,32 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                   const float* __restrict__ g, const float* __restrict__ beta, float* __restrict__ o,
                   float* __restrict__ state, long long state_stride, const int* __restrict__ q_start,
                   const int* __restrict__ q_len, const int* __restrict__ state_slot, int H, int G, int dim, int vdim) {
-    constexpr int DP = 4 * R4 * LANES, R = 4 * R4, COLS = DR_THREADS / LANES, BT = DR_BATCH, CP = COLS < 4 ? 4 : COLS;
+    constexpr int DP = 4 * R4 * LANES, R = 4 * R4, CPT = DR_CPT, COLS = DR_THREADS / LANES * CPT, BT = DR_BATCH;
     // a ring of DR_STAGES stages of BT tokens: the inputs come from DRAM, a microsecond or two away, and a stage is worked
     // through in a fraction of that
     extern __shared__ __align__(16) float ring[];
     typedef float (*RowsDP)[BT][DP];
-    typedef float (*RowsCP)[BT][CP];
+    typedef float (*RowsCP)[BT][COLS];
     typedef float (*RowsB)[BT];
     RowsDP sq = reinterpret_cast<RowsDP>(ring), sk = sq + DR_STAGES, sg = sk + DR_STAGES;
     RowsCP sv = reinterpret_cast<RowsCP>(ring + 3 * DR_STAGES * BT * DP);
-    RowsB sb = reinterpret_cast<RowsB>(ring + 3 * DR_STAGES * BT * DP + DR_STAGES * BT * CP);
+    RowsB sb = reinterpret_cast<RowsB>(ring + 3 * DR_STAGES * BT * DP + DR_STAGES * BT * COLS);
     const int s = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * COLS;
-    const int lane = threadIdx.x & (LANES - 1), cl = threadIdx.x / LANES, col = col0 + cl;
-    const bool live = col < vdim;
+    const int lane = threadIdx.x & (LANES - 1), cg = threadIdx.x / LANES, colA = col0 + cg * CPT;   // this thread's first column
     const int a = q_start[s], len = q_len[s], j = h / (H / G);
     float* S = state + (size_t)state_slot[s] * state_stride + (size_t)h * dim * vdim;
-    float st[R];
+    float st[CPT][R];
 #pragma unroll
-    for (int r4 = 0; r4 < R4; r4++)
+    for (int c = 0; c < CPT; c++)
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            const int i = r4 * 4 * LANES + lane * 4 + c;
-            st[r4 * 4 + c] = (live && i < dim) ? S[(size_t)i * vdim + col] : 0.0f;
-        }
+        for (int r4 = 0; r4 < R4; r4++)
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+                const int i = r4 * 4 * LANES + lane * 4 + x;
+                st[c][r4 * 4 + x] = (colA + c < vdim && i < dim) ? S[(size_t)i * vdim + colA + c] : 0.0f;
+            }
     // 16 bytes a copy where every row starts on a 16-byte boundary (dim and vdim multiples of 4), else 4
-    const bool vec = (dim & 3) == 0 && (vdim & 3) == 0 && COLS >= 4;
+    const bool vec = (dim & 3) == 0 && (vdim & 3) == 0;
     auto fetch = [&](int buf, int t0) {
         const int nb = min(BT, len - t0);
         if (vec) {
@@ -154,43 +157,61 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         __syncthreads();
 #pragma unroll 2
         for (int tt = 0; tt < nb; tt++) {
-            float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+            // a value of q, k, g read from shared memory serves the thread's CPT columns
+            float dot[CPT], acc[CPT], u[CPT];
             float4 kk[R4];
+#pragma unroll
+            for (int c = 0; c < CPT; c++) dot[c] = 0.0f;
 #pragma unroll
             for (int r4 = 0; r4 < R4; r4++) {
                 const float4 gg = *reinterpret_cast<const float4*>(&sg[buf][tt][r4 * 4 * LANES + lane * 4]);
                 kk[r4] = *reinterpret_cast<const float4*>(&sk[buf][tt][r4 * 4 * LANES + lane * 4]);
-                st[r4 * 4 + 0] *= gg.x; st[r4 * 4 + 1] *= gg.y; st[r4 * 4 + 2] *= gg.z; st[r4 * 4 + 3] *= gg.w;
-                d0 = fmaf(st[r4 * 4 + 0], kk[r4].x, d0); d1 = fmaf(st[r4 * 4 + 1], kk[r4].y, d1);
-                d2 = fmaf(st[r4 * 4 + 2], kk[r4].z, d2); d3 = fmaf(st[r4 * 4 + 3], kk[r4].w, d3);
-            }
-            float dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
-            for (int m = 1; m < LANES; m <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
-            const float u = sb[buf][tt] * (sv[buf][tt][cl] - dot);
-            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+                for (int c = 0; c < CPT; c++) {
+                    float* t = &st[c][r4 * 4];
+                    t[0] *= gg.x; t[1] *= gg.y; t[2] *= gg.z; t[3] *= gg.w;
+                    dot[c] = fmaf(t[0], kk[r4].x, dot[c]) + fmaf(t[1], kk[r4].y, fmaf(t[2], kk[r4].z, t[3] * kk[r4].w));
+                }
+            }
+#pragma unroll
+            for (int m = 1; m < LANES; m <<= 1)
+#pragma unroll
+                for (int c = 0; c < CPT; c++) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], m);
+            const float bt = sb[buf][tt];
+#pragma unroll
+            for (int c = 0; c < CPT; c++) { u[c] = bt * (sv[buf][tt][cg * CPT + c] - dot[c]); acc[c] = 0.0f; }
 #pragma unroll
             for (int r4 = 0; r4 < R4; r4++) {
                 const float4 qq = *reinterpret_cast<const float4*>(&sq[buf][tt][r4 * 4 * LANES + lane * 4]);
-                st[r4 * 4 + 0] = fmaf(kk[r4].x, u, st[r4 * 4 + 0]); st[r4 * 4 + 1] = fmaf(kk[r4].y, u, st[r4 * 4 + 1]);
-                st[r4 * 4 + 2] = fmaf(kk[r4].z, u, st[r4 * 4 + 2]); st[r4 * 4 + 3] = fmaf(kk[r4].w, u, st[r4 * 4 + 3]);
-                a0 = fmaf(st[r4 * 4 + 0], qq.x, a0); a1 = fmaf(st[r4 * 4 + 1], qq.y, a1);
-                a2 = fmaf(st[r4 * 4 + 2], qq.z, a2); a3 = fmaf(st[r4 * 4 + 3], qq.w, a3);
-            }
-            float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
-            for (int m = 1; m < LANES; m <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
-            if (lane == 0 && live) o[((size_t)(a + t0 + tt) * H + h) * vdim + col] = acc;
+                for (int c = 0; c < CPT; c++) {
+                    float* t = &st[c][r4 * 4];
+                    t[0] = fmaf(kk[r4].x, u[c], t[0]); t[1] = fmaf(kk[r4].y, u[c], t[1]);
+                    t[2] = fmaf(kk[r4].z, u[c], t[2]); t[3] = fmaf(kk[r4].w, u[c], t[3]);
+                    acc[c] = fmaf(t[0], qq.x, acc[c]) + fmaf(t[1], qq.y, fmaf(t[2], qq.z, t[3] * qq.w));
+                }
+            }
+#pragma unroll
+            for (int m = 1; m < LANES; m <<= 1)
+#pragma unroll
+                for (int c = 0; c < CPT; c++) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], m);
+            if (lane == 0) {
+#pragma unroll
+                for (int c = 0; c < CPT; c++)
+                    if (colA + c < vdim) o[((size_t)(a + t0 + tt) * H + h) * vdim + colA + c] = acc[c];
+            }
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int r4 = 0; r4 < R4; r4++)
+    for (int c = 0; c < CPT; c++)
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-            const int i = r4 * 4 * LANES + lane * 4 + c;
-            if (live && i < dim) S[(size_t)i * vdim + col] = st[r4 * 4 + c];
-        }
+        for (int r4 = 0; r4 < R4; r4++)
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+                const int i = r4 * 4 * LANES + lane * 4 + x;
+                if (colA + c < vdim && i < dim) S[(size_t)i * vdim + colA + c] = st[c][r4 * 4 + x];
+            }
 }
 
 // grid (N, H): o (N, H vdim) float32 -> out in the storage type
@@ -247,8 +268,8 @@ MB_API int mb_delta_rule(const float* q, const float* k, const float* v, const f
     if (G < 1 || H % G || H > 65535 || S > 65535 || dim < 1 || dim > 256 || vdim < 1) return -2;
 #define DR_CASE(LANES, R4)                                                                                                 \
     if (dim <= 4 * R4 * LANES && (lanes == 0 || lanes == LANES)) {                                                         \
-        const int cols = DR_THREADS / LANES, cp = cols < 4 ? 4 : cols;                                                     \
-        const size_t smem = (size_t)DR_STAGES * DR_BATCH * (3 * 4 * R4 * LANES + cp + 1) * sizeof(float);                  \
+        const int cols = DR_THREADS / LANES * DR_CPT;                                                                      \
+        const size_t smem = (size_t)DR_STAGES * DR_BATCH * (3 * 4 * R4 * LANES + cols + 1) * sizeof(float);                \
         static bool configured = false;                                                                                    \
         if (!configured && smem > 48 * 1024) {                                                                             \
             cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<LANES, R4>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
