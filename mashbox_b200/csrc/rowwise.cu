@@ -28,33 +28,73 @@ __global__ void embed_pos_kernel(const int* __restrict__ tokens, const int* __re
     for (int d = threadIdx.x; d < D; d += blockDim.x) x[(size_t)n * D + d] = mb_load(e + d) * scale + mb_load(q + d);
 }
 
-template <typename T>
+// four values of a row at once (D a multiple of 4, 16-byte aligned rows)
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u), __uint_as_float(r.y << 16),
+                       __uint_as_float(r.y & 0xffff0000u));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+}
+
+// VEC: rows are read and written four values at a time; the sums of squares run in the same order either way only
+// within a form, so a model uses one form throughout (the choice depends on D alone).
+template <typename T, bool VEC>
 __global__ void post_norm_add_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ post_w,
                                      float post_eps, const float* __restrict__ next_w, float next_eps, T* __restrict__ normed,
                                      T* __restrict__ copy, int D) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float scratch[32];
     const int n = blockIdx.x;
     float ss = 0.0f;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        const float v = mb_load(delta + (size_t)n * D + d);
-        row[d] = v;
-        ss = fmaf(v, v, ss);
+    if (VEC) {
+        for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
+            const float4 v = load4(delta + (size_t)n * D + d);
+            store4(row + d, v);
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            const float v = mb_load(delta + (size_t)n * D + d);
+            row[d] = v;
+            ss = fmaf(v, v, ss);
+        }
     }
     ss = mb_block_sum(ss, scratch);
     const float r = 1.0f / sqrtf(ss / (float)D + post_eps);
     float s2 = 0.0f;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        const float v = x[(size_t)n * D + d] + row[d] * r * post_w[d];
-        x[(size_t)n * D + d] = v;
-        row[d] = v;
-        s2 = fmaf(v, v, s2);
-        if (copy) mb_store(copy + (size_t)n * D + d, v);
+    if (VEC) {
+        for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
+            const float4 xv = load4(x + (size_t)n * D + d), dv = load4(row + d), w = load4(post_w + d);
+            const float4 v = make_float4(xv.x + dv.x * r * w.x, xv.y + dv.y * r * w.y, xv.z + dv.z * r * w.z, xv.w + dv.w * r * w.w);
+            store4(x + (size_t)n * D + d, v);
+            store4(row + d, v);
+            s2 = fmaf(v.x, v.x, s2); s2 = fmaf(v.y, v.y, s2); s2 = fmaf(v.z, v.z, s2); s2 = fmaf(v.w, v.w, s2);
+            if (copy) store4(copy + (size_t)n * D + d, v);
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            const float v = x[(size_t)n * D + d] + row[d] * r * post_w[d];
+            x[(size_t)n * D + d] = v;
+            row[d] = v;
+            s2 = fmaf(v, v, s2);
+            if (copy) mb_store(copy + (size_t)n * D + d, v);
+        }
     }
     if (!normed) return;
     s2 = mb_block_sum(s2, scratch);
     const float r2 = 1.0f / sqrtf(s2 / (float)D + next_eps);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) mb_store(normed + (size_t)n * D + d, row[d] * r2 * next_w[d]);
+    if (VEC) {
+        for (int d = threadIdx.x * 4; d < D; d += blockDim.x * 4) {
+            const float4 v = load4(row + d), w = load4(next_w + d);
+            store4(normed + (size_t)n * D + d, make_float4(v.x * r2 * w.x, v.y * r2 * w.y, v.z * r2 * w.z, v.w * r2 * w.w));
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) mb_store(normed + (size_t)n * D + d, row[d] * r2 * next_w[d]);
+    }
 }
 
 template <typename T>
@@ -162,8 +202,15 @@ static int post_norm_add_launch(float* x, const T* delta, const float* post_w, f
                                 float next_eps, T* normed, T* copy, int N, int D, cudaStream_t st) {
     if (N == 0) return 0;
     if (D < 1 || D > 12000 || (normed && !next_w)) return -2;
-    post_norm_add_kernel<T><<<N, row_threads(D), (size_t)D * sizeof(float), st>>>(x, delta, post_w, post_eps, next_w,
-                                                                                  next_eps, normed, copy, D);
+    const bool vec = D % 4 == 0 && !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(delta) |
+                                     reinterpret_cast<uintptr_t>(post_w) | reinterpret_cast<uintptr_t>(next_w) |
+                                     reinterpret_cast<uintptr_t>(normed) | reinterpret_cast<uintptr_t>(copy)) & 15);
+    if (vec)
+        post_norm_add_kernel<T, true><<<N, D >= 2048 ? 256 : D >= 512 ? 128 : 64, (size_t)D * sizeof(float), st>>>(
+            x, delta, post_w, post_eps, next_w, next_eps, normed, copy, D);
+    else
+        post_norm_add_kernel<T, false><<<N, row_threads(D), (size_t)D * sizeof(float), st>>>(x, delta, post_w, post_eps, next_w,
+                                                                                             next_eps, normed, copy, D);
     MB_LAUNCH_CHECK();
     return 0;
 }
