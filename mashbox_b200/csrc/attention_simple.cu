@@ -4,16 +4,16 @@
 // the window, never on how tokens were cut into steps or which pages hold the keys.
 #include "common.cuh"
 
-#define SIMPLE_MAX_HD 256
+#define SIMPLE_MAX_HD 512          // the widest rows (two instantiations: up to 256, and up to this)
 #define WARPS 4
 
-template <typename T>
+template <typename T, int MAXHD>
 __global__ void __launch_bounds__(WARPS * 32) attn_simple_kernel(
     const T* __restrict__ q, int q_stride, T* __restrict__ out, const int* __restrict__ positions,
     const int* __restrict__ tok_seq, const int* __restrict__ table, int max_blocks, const T* __restrict__ kpool,
     const T* __restrict__ vpool, int N, int H, int KV, int HD, int page, int num_pages, int window, float scale,
     int* err) {
-    __shared__ float qs[WARPS][SIMPLE_MAX_HD];
+    __shared__ float qs[WARPS][MAXHD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
     if (item >= (long long)N * H) return;
@@ -26,9 +26,9 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simple_kernel(
     __syncwarp();
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     float m = -INFINITY, l = 0.0f;
-    float acc[SIMPLE_MAX_HD / 32];
+    float acc[MAXHD / 32];
 #pragma unroll
-    for (int i = 0; i < SIMPLE_MAX_HD / 32; i++) acc[i] = 0.0f;
+    for (int i = 0; i < MAXHD / 32; i++) acc[i] = 0.0f;
     for (int base = lo; base <= pos; base += 32) {
         const int kp = base + lane;
         const bool valid = kp <= pos;
@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simple_kernel(
         const float corr = expf(m - m_new);
         l = l * corr + mb_warp_sum(p);
 #pragma unroll
-        for (int i = 0; i < SIMPLE_MAX_HD / 32; i++) acc[i] *= corr;
+        for (int i = 0; i < MAXHD / 32; i++) acc[i] *= corr;
         const int cnt = min(32, pos - base + 1);
         for (int j = 0; j < cnt; j++) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simple_kernel(
             if (oj < 0) continue;
             const T* vr = vpool + oj;
 #pragma unroll
-            for (int i = 0; i < SIMPLE_MAX_HD / 32; i++) {
+            for (int i = 0; i < MAXHD / 32; i++) {
                 const int d = lane + 32 * i;
                 if (d < HD) acc[i] = fmaf(pj, mb_load(vr + d), acc[i]);
             }
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simple_kernel(
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
     T* o = out + (size_t)n * H * HD + (size_t)h * HD;
 #pragma unroll
-    for (int i = 0; i < SIMPLE_MAX_HD / 32; i++) {
+    for (int i = 0; i < MAXHD / 32; i++) {
         const int d = lane + 32 * i;
         if (d < HD) mb_store(o + d, acc[i] * inv);
     }
@@ -85,9 +85,14 @@ static int attn_simple_launch(const void* q, int q_stride, void* out, const int*
     if (N == 0) return 0;
     if (HD > SIMPLE_MAX_HD || HD < 1 || KV < 1 || H % KV) return -2;
     const long long items = (long long)N * H;
-    attn_simple_kernel<T><<<(unsigned)((items + WARPS - 1) / WARPS), WARPS * 32, 0, st>>>(
-        (const T*)q, q_stride, (T*)out, positions, tok_seq, table, max_blocks, (const T*)kpool, (const T*)vpool, N, H,
-        KV, HD, page, num_pages, window, scale, err);
+    if (HD <= 256)
+        attn_simple_kernel<T, 256><<<(unsigned)((items + WARPS - 1) / WARPS), WARPS * 32, 0, st>>>(
+            (const T*)q, q_stride, (T*)out, positions, tok_seq, table, max_blocks, (const T*)kpool, (const T*)vpool, N, H,
+            KV, HD, page, num_pages, window, scale, err);
+    else
+        attn_simple_kernel<T, SIMPLE_MAX_HD><<<(unsigned)((items + WARPS - 1) / WARPS), WARPS * 32, 0, st>>>(
+            (const T*)q, q_stride, (T*)out, positions, tok_seq, table, max_blocks, (const T*)kpool, (const T*)vpool, N, H,
+            KV, HD, page, num_pages, window, scale, err);
     MB_LAUNCH_CHECK();
     return 0;
 }

@@ -44,7 +44,18 @@ SUF_V = SufopelConfig("Sufopel", width=128, vocab=301, max_positions=640, embedd
     SufopelLayer("channel_delta", delta(4, 4, 64, 32, 3, 16, 8), DenseFF(192)),
     SufopelLayer("latent_attention", latent(4, 32, 32, 64, 128, 0.18), DenseFF(96)),
     SufopelLayer("latent_attention", latent(8, 16, 32, 32, 64, 0.25, kv_from=0), RoutedFF(32, 0.5, 4, 2, 2, 1))))
-CONFIGS = {"T": (SUF_T, 11, 8), "U": (SUF_U, 12, 16), "V": (SUF_V, 13, 16)}       # config, seed, page size
+# W: delta layers only -- the model keeps nothing per position, the cache manager has no group and no page is ever taken
+SUF_W = SufopelConfig("Sufopel", width=48, vocab=61, max_positions=448, embedding_scale=1.5, logit_scale=0.5,
+                      norm_eps=1e-5, side_dim=4, layers=(
+    SufopelLayer("channel_delta", delta(2, 1, 16, 8, 3, 4, 4), DenseFF(64)),
+    SufopelLayer("channel_delta", delta(1, 1, 32, 48, 2, 8, 2), RoutedFF(16, 1.2, 4, 2, 2, 2))))
+# X: latent layers only (no state), latents of 288 values: wider than any tensor-core attention kernel takes
+SUF_X = SufopelConfig("Sufopel", width=80, vocab=73, max_positions=448, embedding_scale=1.0, logit_scale=1.0,
+                      norm_eps=1e-6, side_dim=None, layers=(
+    SufopelLayer("latent_attention", latent(2, 24, 40, 32, 288, 0.2), DenseFF(96)),
+    SufopelLayer("latent_attention", latent(5, 8, 8, 16, 288, 0.35, kv_from=0), None)))
+CONFIGS = {"T": (SUF_T, 11, 8), "U": (SUF_U, 12, 16), "V": (SUF_V, 13, 16), "W": (SUF_W, 14, 32),
+           "X": (SUF_X, 15, 8)}       # config, seed, page size
 
 # Readers near 1/sqrt(fan in), writers into the stream small; filters, decays and corrections of order 0.3 to 1 so
 # that they matter; the router wide enough that the chosen experts are seldom a close call.
