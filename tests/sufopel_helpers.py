@@ -54,8 +54,15 @@ SUF_X = SufopelConfig("Sufopel", width=80, vocab=73, max_positions=448, embeddin
                       norm_eps=1e-6, side_dim=None, layers=(
     SufopelLayer("latent_attention", latent(2, 24, 40, 32, 288, 0.2), DenseFF(96)),
     SufopelLayer("latent_attention", latent(5, 8, 8, 16, 288, 0.35, kv_from=0), None)))
+# Y: more heads than a decode tile of the tensor-core attention kernels has rows (20 and 24 over one row per position):
+#    a single decoded token is a prompt-form tile, which the plan cuts along the keys
+SUF_Y = SufopelConfig("Sufopel", width=64, vocab=97, max_positions=448, embedding_scale=1.0, logit_scale=1.5,
+                      norm_eps=1e-5, side_dim=None, layers=(
+    SufopelLayer("latent_attention", latent(20, 8, 8, 32, 64, 0.3), DenseFF(64)),
+    SufopelLayer("channel_delta", delta(2, 2, 16, 16, 2, 4, 4), None),
+    SufopelLayer("latent_attention", latent(24, 8, 4, 16, 64, 0.25, kv_from=0), DenseFF(48))))
 CONFIGS = {"T": (SUF_T, 11, 8), "U": (SUF_U, 12, 16), "V": (SUF_V, 13, 16), "W": (SUF_W, 14, 32),
-           "X": (SUF_X, 15, 8)}       # config, seed, page size
+           "X": (SUF_X, 15, 8), "Y": (SUF_Y, 16, 16)}       # config, seed, page size
 
 # Readers near 1/sqrt(fan in), writers into the stream small; filters, decays and corrections of order 0.3 to 1 so
 # that they matter; the router wide enough that the chosen experts are seldom a close call.

@@ -440,7 +440,8 @@ def test_unequal_requests_side_by_side_with_pages_and_slots_used_again(tmp_path_
     assert runner.cache.free_pages() == [runner.cache.num_pages] * len(runner.cache.groups)
 
 
-@pytest.mark.parametrize("name,dtype", [("T", "float32"), ("T", "bfloat16"), ("V", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("T", "float32"), ("T", "bfloat16"), ("V", "bfloat16"), ("Y", "bfloat16"),
+                                        ("W", "float32")])
 def test_long_decoding(tmp_path_factory, name, dtype):
     """a short prompt and 380 tokens one by one (graphs replayed), two requests side by side"""
     folder, runner = runner_for(tmp_path_factory.mktemp("m"), name, dtype, 896)
