@@ -22,6 +22,21 @@
 #define DR_BATCH 8
 #define DR_STAGES 4
 
+// two floats in one 64-bit register pair, and the fused multiply-add on such pairs
+__device__ __forceinline__ uint64_t dr_pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void dr_unpack2(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t dr_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 // 4 bytes from global to shared memory without a register in between; size 0: the destination is set to zero
 __device__ __forceinline__ void dr_cp16(float* smem, const float* gmem, int size) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(size));
@@ -94,15 +109,17 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     const int lane = threadIdx.x & (LANES - 1), cg = threadIdx.x / LANES, colA = col0 + cg * CPT;   // this thread's first column
     const int a = q_start[s], len = q_len[s], j = h / (H / G);
     float* S = state + (size_t)state_slot[s] * state_stride + (size_t)h * dim * vdim;
-    float st[CPT][R];
+    uint64_t st[CPT][R / 2];                // the state values in pairs: channels (i, i + 1) of one column
 #pragma unroll
     for (int c = 0; c < CPT; c++)
 #pragma unroll
         for (int r4 = 0; r4 < R4; r4++)
 #pragma unroll
-            for (int x = 0; x < 4; x++) {
+            for (int x = 0; x < 4; x += 2) {
                 const int i = r4 * 4 * LANES + lane * 4 + x;
-                st[c][r4 * 4 + x] = (colA + c < vdim && i < dim) ? S[(size_t)i * vdim + colA + c] : 0.0f;
+                const bool in = colA + c < vdim;
+                st[c][r4 * 2 + x / 2] = dr_pack2((in && i < dim) ? S[(size_t)i * vdim + colA + c] : 0.0f,
+                                                 (in && i + 1 < dim) ? S[(size_t)(i + 1) * vdim + colA + c] : 0.0f);
             }
     // 16 bytes a copy where every row starts on a 16-byte boundary (dim and vdim multiples of 4), else 4
     const bool vec = (dim & 3) == 0 && (vdim & 3) == 0;
@@ -157,21 +174,34 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         __syncthreads();
 #pragma unroll 2
         for (int tt = 0; tt < nb; tt++) {
-            // a value of q, k, g read from shared memory serves the thread's CPT columns
+            // a value of q, k, g read from shared memory serves the thread's CPT columns; the arithmetic runs on pairs
+            // of floats (fma.rn.f32x2: one issue slot, two results, each rounded as the single one is)
+            uint64_t dsum[CPT][2], asum[CPT][2], k2[R4][2];
             float dot[CPT], acc[CPT], u[CPT];
-            float4 kk[R4];
+            const uint64_t zero2 = dr_pack2(0.0f, 0.0f);
 #pragma unroll
-            for (int c = 0; c < CPT; c++) dot[c] = 0.0f;
+            for (int c = 0; c < CPT; c++) dsum[c][0] = dsum[c][1] = asum[c][0] = asum[c][1] = zero2;
 #pragma unroll
             for (int r4 = 0; r4 < R4; r4++) {
                 const float4 gg = *reinterpret_cast<const float4*>(&sg[buf][tt][r4 * 4 * LANES + lane * 4]);
-                kk[r4] = *reinterpret_cast<const float4*>(&sk[buf][tt][r4 * 4 * LANES + lane * 4]);
+                const float4 kk = *reinterpret_cast<const float4*>(&sk[buf][tt][r4 * 4 * LANES + lane * 4]);
+                const uint64_t g01 = dr_pack2(gg.x, gg.y), g23 = dr_pack2(gg.z, gg.w);
+                k2[r4][0] = dr_pack2(kk.x, kk.y);
+                k2[r4][1] = dr_pack2(kk.z, kk.w);
 #pragma unroll
                 for (int c = 0; c < CPT; c++) {
-                    float* t = &st[c][r4 * 4];
-                    t[0] *= gg.x; t[1] *= gg.y; t[2] *= gg.z; t[3] *= gg.w;
-                    dot[c] = fmaf(t[0], kk[r4].x, dot[c]) + fmaf(t[1], kk[r4].y, fmaf(t[2], kk[r4].z, t[3] * kk[r4].w));
+                    st[c][r4 * 2] = dr_fma2(st[c][r4 * 2], g01, zero2);               // the decay: a product, rounded once
+                    st[c][r4 * 2 + 1] = dr_fma2(st[c][r4 * 2 + 1], g23, zero2);
+                    dsum[c][0] = dr_fma2(st[c][r4 * 2], k2[r4][0], dsum[c][0]);
+                    dsum[c][1] = dr_fma2(st[c][r4 * 2 + 1], k2[r4][1], dsum[c][1]);
                 }
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; c++) {
+                float a0, a1, a2, a3;
+                dr_unpack2(dsum[c][0], a0, a1);
+                dr_unpack2(dsum[c][1], a2, a3);
+                dot[c] = (a0 + a1) + (a2 + a3);
             }
 #pragma unroll
             for (int m = 1; m < LANES; m <<= 1)
@@ -179,17 +209,26 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                 for (int c = 0; c < CPT; c++) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], m);
             const float bt = sb[buf][tt];
 #pragma unroll
-            for (int c = 0; c < CPT; c++) { u[c] = bt * (sv[buf][tt][cg * CPT + c] - dot[c]); acc[c] = 0.0f; }
+            for (int c = 0; c < CPT; c++) u[c] = bt * (sv[buf][tt][cg * CPT + c] - dot[c]);
 #pragma unroll
             for (int r4 = 0; r4 < R4; r4++) {
                 const float4 qq = *reinterpret_cast<const float4*>(&sq[buf][tt][r4 * 4 * LANES + lane * 4]);
+                const uint64_t q01 = dr_pack2(qq.x, qq.y), q23 = dr_pack2(qq.z, qq.w);
 #pragma unroll
                 for (int c = 0; c < CPT; c++) {
-                    float* t = &st[c][r4 * 4];
-                    t[0] = fmaf(kk[r4].x, u[c], t[0]); t[1] = fmaf(kk[r4].y, u[c], t[1]);
-                    t[2] = fmaf(kk[r4].z, u[c], t[2]); t[3] = fmaf(kk[r4].w, u[c], t[3]);
-                    acc[c] = fmaf(t[0], qq.x, acc[c]) + fmaf(t[1], qq.y, fmaf(t[2], qq.z, t[3] * qq.w));
+                    const uint64_t u2 = dr_pack2(u[c], u[c]);
+                    st[c][r4 * 2] = dr_fma2(k2[r4][0], u2, st[c][r4 * 2]);
+                    st[c][r4 * 2 + 1] = dr_fma2(k2[r4][1], u2, st[c][r4 * 2 + 1]);
+                    asum[c][0] = dr_fma2(st[c][r4 * 2], q01, asum[c][0]);
+                    asum[c][1] = dr_fma2(st[c][r4 * 2 + 1], q23, asum[c][1]);
                 }
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; c++) {
+                float a0, a1, a2, a3;
+                dr_unpack2(asum[c][0], a0, a1);
+                dr_unpack2(asum[c][1], a2, a3);
+                acc[c] = (a0 + a1) + (a2 + a3);
             }
 #pragma unroll
             for (int m = 1; m < LANES; m <<= 1)
@@ -208,9 +247,12 @@ delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 #pragma unroll
         for (int r4 = 0; r4 < R4; r4++)
 #pragma unroll
-            for (int x = 0; x < 4; x++) {
+            for (int x = 0; x < 4; x += 2) {
                 const int i = r4 * 4 * LANES + lane * 4 + x;
-                if (colA + c < vdim && i < dim) S[(size_t)i * vdim + colA + c] = st[c][r4 * 4 + x];
+                float lo, hi;
+                dr_unpack2(st[c][r4 * 2 + x / 2], lo, hi);
+                if (colA + c < vdim && i < dim) S[(size_t)i * vdim + colA + c] = lo;
+                if (colA + c < vdim && i + 1 < dim) S[(size_t)(i + 1) * vdim + colA + c] = hi;
             }
 }
 
