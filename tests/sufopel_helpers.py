@@ -61,8 +61,16 @@ SUF_Y = SufopelConfig("Sufopel", width=64, vocab=97, max_positions=448, embeddin
     SufopelLayer("latent_attention", latent(20, 8, 8, 32, 64, 0.3), DenseFF(64)),
     SufopelLayer("channel_delta", delta(2, 2, 16, 16, 2, 4, 4), None),
     SufopelLayer("latent_attention", latent(24, 8, 4, 16, 64, 0.25, kv_from=0), DenseFF(48))))
+# Z: sizes that are multiples of neither 8 nor 16, so that no 16-byte form of any kernel applies: width 100, heads of
+#    12 x 20 and 10 x 6, latents of 28 from a query latent of 20, experts of 28, a token input of 6, a page of 5 positions
+SUF_Z = SufopelConfig("Sufopel", width=100, vocab=53, max_positions=448, embedding_scale=0.75, logit_scale=1.25,
+                      norm_eps=1e-5, side_dim=6, layers=(
+    SufopelLayer("channel_delta", delta(3, 3, 12, 20, 3, 5, 7), RoutedFF(28, 0.9, 6, 2, 3, 2)),
+    SufopelLayer("latent_attention", latent(3, 10, 6, 20, 28, 0.3), DenseFF(44)),
+    SufopelLayer("channel_delta", delta(2, 1, 10, 6, 5, 3, 3), None),
+    SufopelLayer("latent_attention", latent(5, 6, 10, 12, 28, 0.4, kv_from=1), RoutedFF(12, 2.0, 5, 3, 1, 1))))
 CONFIGS = {"T": (SUF_T, 11, 8), "U": (SUF_U, 12, 16), "V": (SUF_V, 13, 16), "W": (SUF_W, 14, 32),
-           "X": (SUF_X, 15, 8), "Y": (SUF_Y, 16, 16)}       # config, seed, page size
+           "X": (SUF_X, 15, 8), "Y": (SUF_Y, 16, 16), "Z": (SUF_Z, 17, 5)}       # config, seed, page size
 
 # Readers near 1/sqrt(fan in), writers into the stream small; filters, decays and corrections of order 0.3 to 1 so
 # that they matter; the router wide enough that the chosen experts are seldom a close call.
